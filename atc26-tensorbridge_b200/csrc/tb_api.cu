@@ -65,6 +65,41 @@ int make_map_u8(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows
     return TB_OK;
 }
 
+// Encoding a tensor map costs a driver call of a microsecond or two, and a layer meets the same few (buffer, shape, tile)
+// combinations over and over.  The encoded bytes are a pure function of the arguments, so a small direct-mapped cache
+// per thread returns them without the call.
+struct MapKey {
+    const void* base;
+    uint64_t cols, rows, row_stride;
+    uint32_t box_cols, box_rows;
+    int swizzle;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && cols == o.cols && rows == o.rows && row_stride == o.row_stride && box_cols == o.box_cols &&
+               box_rows == o.box_rows && swizzle == o.swizzle;
+    }
+};
+
+int cached_map_u8(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride, uint32_t box_cols,
+                  uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    constexpr int kEntries = 256;
+    struct Entry { MapKey key; CUtensorMap map; bool used; };
+    thread_local Entry* table = nullptr;
+    if (table == nullptr) table = new Entry[kEntries]();
+    const MapKey key = {base, cols, rows, row_stride, box_cols, box_rows, static_cast<int>(swizzle)};
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+    h = (h ^ (rows * 0x9E3779B97F4A7C15ull) ^ (cols << 17) ^ (static_cast<uint64_t>(box_rows) << 40) ^ static_cast<uint64_t>(swizzle)) * 0xD6E8FEB86659FD93ull;
+    Entry& e = table[(h >> 32) % kEntries];
+    if (e.used && e.key == key) {
+        *map = e.map;
+        return TB_OK;
+    }
+    if (int rc = make_map_u8(map, base, cols, rows, row_stride, box_cols, box_rows, swizzle)) return rc;
+    e.key = key;
+    e.map = *map;
+    e.used = true;
+    return TB_OK;
+}
+
 struct DeviceInfo {
     int num_sms = 0;
     int smem_optin = 0;
@@ -198,6 +233,12 @@ int rule(const tb_problem& pr, tb_config* cfg) {
     return TB_OK;
 }
 
+// Bytes of K-split scratch: the header words, then one 8-byte {partial sum, tag} word per element of every split.
+long long split_scratch_bytes(long long m, long long n, int block_m, int splits) {
+    const long long tiles = static_cast<long long>(ceil_div(m, block_m)) * (pad128(n) / 128);
+    return tb::kEpochCells * 4 + tiles * splits * block_m * 128 * 8;
+}
+
 int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routing, const tb_config* cfg) {
     if (a == nullptr || cfg == nullptr) return fail(TB_ERR_INVALID, "null arguments");
     if (a->rows < 0 || a->n <= 0 || a->k <= 0) return fail(TB_ERR_INVALID, "bad shape rows=%lld n=%lld k=%lld",
@@ -265,6 +306,9 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     p.num_experts = experts;
     p.top_k = routing != nullptr && layout == TB_LAYOUT_INDEXED ? routing->top_k : 1;
     p.status = a->status;
+    // Wait budget in SM cycles: the default is about a second; `wait_us` counts at 2 GHz (the clock tops out below).
+    p.wait_cycles = a->wait_us > 0 ? static_cast<long long>(a->wait_us) * 2000 : tb::kWaitCycles;
+    if (a->only_split < 0) return fail(TB_ERR_INVALID, "only_split must not be negative");
     const int max_bridged = tb::max_bridged_stages(bm, a->group_scales != 0);
     p.bridged_stages = cfg->stream_k_aligned > 0 ? cfg->stream_k_aligned : std::min(4, max_bridged);
     if (p.bridged_stages < 2 || p.bridged_stages > max_bridged)
@@ -301,12 +345,14 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
         p.splits = std::max(1, static_cast<int>(cfg->use_stream_k));
         p.splits = std::min(p.splits, p.k_blocks);
         if (a->group_scales) p.splits = 1;
+        if (a->only_split > p.splits) return fail(TB_ERR_INVALID, "only_split %d exceeds the %d K splits", a->only_split, p.splits);
+        p.only_split = p.splits > 1 ? a->only_split : 0;
         const long long tiles = static_cast<long long>(p.m_blocks) * p.n_tiles;
         if (p.splits > 1) {
-            if (tiles > 128) return fail(TB_ERR_INVALID, "K splits need at most 128 output tiles, got %lld", tiles);
+            if (tiles > tb::kMaxSplitTiles) return fail(TB_ERR_INVALID, "K splits need at most %d output tiles, got %lld", tb::kMaxSplitTiles, tiles);
             if (a->workspace == nullptr) return fail(TB_ERR_INVALID, "K splits need a workspace");
             if (reinterpret_cast<uintptr_t>(a->workspace) % 8 != 0) return fail(TB_ERR_INVALID, "workspace must be 8-byte aligned");
-            const long long need = tb::kEpochCells * 4 + tiles * p.splits * bm * 128 * 8;
+            const long long need = split_scratch_bytes(a->rows, a->n, bm, p.splits);
             if (a->workspace_bytes < need) return fail(TB_ERR_INVALID, "workspace of %lld bytes is below the %lld needed", (long long)a->workspace_bytes, need);
         }
         units = tiles * p.splits;
@@ -353,13 +399,13 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     }
     // Tensor maps: activations (128-byte swizzle, rows past the end read as zero) and weight scales.
     if (layout != TB_LAYOUT_INDEXED || p.a_gathered) {
-        if (int rc = make_map_u8(&p.map_a, act_base, static_cast<uint64_t>(a->k), act_rows,
+        if (int rc = cached_map_u8(&p.map_a, act_base, static_cast<uint64_t>(a->k), act_rows,
                                  static_cast<uint64_t>(a->k), 128, static_cast<uint32_t>(bm), CU_TENSOR_MAP_SWIZZLE_128B))
             return rc;
     }
     if (!a->group_scales) {
         const uint64_t sf_rows = static_cast<uint64_t>(std::max(experts, 1)) * (p.k_pad / 16);
-        if (int rc = make_map_u8(&p.map_sf, a->scale, static_cast<uint64_t>(p.n_pad), sf_rows, static_cast<uint64_t>(p.n_pad),
+        if (int rc = cached_map_u8(&p.map_sf, a->scale, static_cast<uint64_t>(p.n_pad), sf_rows, static_cast<uint64_t>(p.n_pad),
                                  128, 8, CU_TENSOR_MAP_SWIZZLE_NONE))
             return rc;
     }
@@ -460,9 +506,8 @@ int tb_select_config(const tb_problem* problem, tb_config* config) {
 }
 
 int64_t tb_workspace_bytes(int64_t m, int64_t n, const tb_config* config) {
-    if (config == nullptr || config->use_stream_k <= 1 || m <= 0 || n <= 0) return 0;
-    const long long tiles = static_cast<long long>(ceil_div(m, config->block_m)) * (pad128(n) / 128);
-    return tb::kEpochCells * 4 + tiles * config->use_stream_k * config->block_m * 128 * 8;
+    if (config == nullptr || config->use_stream_k <= 1 || m <= 0 || n <= 0 || !valid_block_m(config->block_m)) return 0;
+    return split_scratch_bytes(m, n, config->block_m, config->use_stream_k);
 }
 
 int tb_quantize_fp8(void* stream, const void* x, int x_dtype, int64_t x_stride, int64_t m, int64_t k, int mode, void* q,
@@ -595,7 +640,11 @@ int tb_gemm_dense(void* stream, const tb_gemm_args* args, const tb_config* confi
 
 int tb_gemm_dense_static_scratch(void* stream, const tb_gemm_args* args, const tb_config* config) {
     if (args == nullptr || config == nullptr) return fail(TB_ERR_INVALID, "null arguments");
-    const long long need = tb_workspace_bytes(args->rows, args->n, config);
+    if (!valid_block_m(config->block_m)) return fail(TB_ERR_INVALID, "block_m must be 16, 32, 64, 128, 192 or 256, got %d", config->block_m);
+    // The splits the launch will really make: never more than K blocks, none with [1,128] scales.
+    const int k_blocks = pad128(std::max<long long>(args->k, 1)) / 128;
+    const int splits = args->group_scales ? 1 : std::min(std::max(1, static_cast<int>(config->use_stream_k)), k_blocks);
+    const long long need = splits > 1 && args->rows > 0 && args->n > 0 ? split_scratch_bytes(args->rows, args->n, config->block_m, splits) : 0;
     if (need > kStaticScratchBytes)
         return fail(TB_ERR_INVALID, "this launch needs %lld bytes of split-K scratch; the library's static scratch holds %lld "
                     "(use fewer K splits, or tb_gemm_dense with a caller-owned workspace)", need, kStaticScratchBytes);

@@ -43,7 +43,8 @@ constexpr int kMaxBridgedStages = 8;
 constexpr int kTileCols = 32;  // tensor-memory columns of one bridged FP8 tile: 128 K values, four per column
 constexpr int kTmemCols = 512;
 constexpr int kMaxAccSets = 8;
-constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K workspace, one per output tile (at most 128 used)
+constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K workspace: [0] launch sequence, [1] CTAs arrived
+constexpr int kMaxSplitTiles = 128;  // output tiles of a K-split launch: the tile index takes 7 bits of a tag
 constexpr int kTransposeBytes = 16 * 32 * 2;  // an epilogue warp's 16-column chunk as BF16 [token][channel]
 constexpr int kBarrierBytes = 832;     // 4 * 16 + 2 * 8 + 2 * 8 + 1 barriers of 8 bytes, padded
 
@@ -71,7 +72,7 @@ struct alignas(64) GemmParams {
     const uint8_t* scale;
     const float* global_scale;
     int* locks;
-    float* workspace;  // split-K: kEpochCells words of tile epochs, then {value, tag} words of the partial sums
+    float* workspace;  // split-K: kEpochCells header words (launch sequence, arrival count), then {value, tag} words
     __nv_bfloat16* d;
     long long rows;  // rows of `a`
     int n, k, n_pad, k_pad;
@@ -90,6 +91,8 @@ struct alignas(64) GemmParams {
     const int* num_tokens_padded;
     long long sorted_capacity;
     int* status;
+    long long wait_cycles;  // budget of every bounded wait
+    int only_split;         // test hook: s + 1 runs only the units of K split s (0 = all)
 };
 
 // One unit of work: one 128-channel tile x BM tokens over a K-block range.
@@ -99,8 +102,9 @@ struct Unit {
     int row0;        // first row of `a` (contiguous / masked / dense) or first slot of sorted_ids (indexed)
     int rows_valid;  // rows of the tile that exist
     int kb0, kb1;    // K-block range
-    int tile;        // dense tile index (split-K counter slot)
+    int tile;        // dense tile index (slot of its partial sums in the split-K workspace)
     int split;
+    bool skip;       // test hook (GemmParams::only_split): the unit is left out by every role
 };
 
 // Accumulator sets in tensor memory.  Per-token scales: two while they leave room for two bridged tiles (one set drains
@@ -301,6 +305,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
     auto decode = [&](int u) {
         Unit t;
         t.split = 0;
+        t.skip = false;
         t.kb0 = 0;
         t.kb1 = p.k_blocks;
         t.expert = 0;
@@ -315,6 +320,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             // of set-up per unit.
             t.kb0 = static_cast<int>(static_cast<unsigned>(t.split) * static_cast<unsigned>(p.k_blocks) / static_cast<unsigned>(p.splits));
             t.kb1 = static_cast<int>(static_cast<unsigned>(t.split + 1) * static_cast<unsigned>(p.k_blocks) / static_cast<unsigned>(p.splits));
+            t.skip = p.only_split != 0 && t.split != p.only_split - 1;
         } else {
             const int g = u / n_groups;
             t.nt = u - g * n_groups;
@@ -357,6 +363,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             [[maybe_unused]] const uint32_t loop_begin = TB_CLOCK();
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
                 const Unit t = decode(u);
+                if (t.skip) continue;
                 const uint8_t* codes =
                     p.weight + ((static_cast<long long>(t.expert) * p.n_tiles + t.nt) * p.k_blocks + t.kb0) * kBlockBytes;
                 // group scales: [E, K/128, n_pad, 8] bytes, 1 KB per (K block, channel tile); else a TMA box of the
@@ -367,7 +374,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                 const int sf_x = t.nt * 128;
                 for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
-                    if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitWeightEmpty)) { ok = false; break; }
+                    if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitWeightEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     waited += TB_CLOCK() - w0;
                     mbar_arrive_expect_tx(full, kWeightRawBytes);
                     bulk_load(stage, codes, kBlockBytes, full);
@@ -407,9 +414,10 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                 bool ok = true;
                 for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
                     const Unit t = decode(u);
+                    if (t.skip) continue;
                     int x = t.kb0 * 128;
                     for (int kb = t.kb0; kb < t.kb1; ++kb) {
-                        if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitTokenEmpty)) { ok = false; break; }
+                        if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitTokenEmpty, 0, p.wait_cycles)) { ok = false; break; }
                         if (dense && u == static_cast<int>(blockIdx.x) && kb == t.kb0) pdl_wait_prior_grid();
                         mbar_arrive_expect_tx(full, kActBytes);
                         tma_load_2d(stage, &p.map_a, x, t.row0, full);
@@ -427,6 +435,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             bool ok = true;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
                 const Unit t = decode(u);
+                if (t.skip) continue;
                 // Source row of every tile row (-1 = padding), once per tile: route id / top_k.
                 __syncwarp();
                 for (int i = lane; i < BM; i += 32) {
@@ -435,7 +444,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                 }
                 __syncwarp();
                 for (int kb = t.kb0; kb < t.kb1; ++kb) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(a_empty(rs), phase ^ 1u, abort_flag, kWaitTokenEmpty))) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(a_empty(rs), phase ^ 1u, abort_flag, kWaitTokenEmpty, 0, p.wait_cycles))) { ok = false; break; }
                     const uint32_t stage = tokens0_u32 + rs * L.token_stage;
                     // Row gather: 8 chunks of 16 bytes per row, written through the 128-byte swizzle.
                     const int chunk = lane & 7;
@@ -472,19 +481,20 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             [[maybe_unused]] uint32_t waited = 0, blocks = 0, loop_begin = 0;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
                 const Unit t = decode(u);
+                if (t.skip) continue;
                 if constexpr (!kGroupScales) {
-                    if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty)) { ok = false; break; }
+                    if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
                 }
                 for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if constexpr (kGroupScales) {
-                        if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty)) { ok = false; break; }
+                        if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     }
                     [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
                     {   // both polls in flight at once; the bounded waits only when one of them is not there yet
                         const bool tokens_in = mbar_try_wait(t_full, tphase), bridged_in = mbar_try_wait(b_full, bphase);
-                        if (!tokens_in && !mbar_wait(t_full, tphase, abort_flag, kWaitTokenFull)) { ok = false; break; }
-                        if (!bridged_in && !mbar_wait(b_full, bphase, abort_flag, kWaitBridgedFull)) { ok = false; break; }
+                        if (!tokens_in && !mbar_wait(t_full, tphase, abort_flag, kWaitTokenFull, 0, p.wait_cycles)) { ok = false; break; }
+                        if (!bridged_in && !mbar_wait(b_full, bphase, abort_flag, kWaitBridgedFull, 0, p.wait_cycles)) { ok = false; break; }
                     }
                     if (blocks++ == 0) { loop_begin = TB_CLOCK(); TB_PHASE(5); } else { waited += TB_CLOCK() - w0; }
                     tc_fence_after_sync();
@@ -539,6 +549,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
         [[maybe_unused]] uint32_t waited_raw = 0, waited_empty = 0, blocks = 0, loop_begin = 0;
         for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
             const Unit t = decode(u);
+            if (t.skip) continue;
             for (int kb = t.kb0; kb < t.kb1; ++kb) {
                 if (kTurns > 1) {
                     if (turn != 0) { --turn; continue; }
@@ -546,7 +557,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                 }
                 // The tensor-memory stores below are warp-wide instructions: the warp must agree on every wait's outcome.
                 [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
-                if (!__all_sync(0xffffffffu, mbar_wait(w_full(rs), rphase, abort_flag, kWaitWeightFull))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(w_full(rs), rphase, abort_flag, kWaitWeightFull, 0, p.wait_cycles))) { ok = false; break; }
                 if (blocks++ == 0) { loop_begin = TB_CLOCK(); if (warp == kEpilogueWarps && lane == 0) TB_PHASE(4); } else { waited_raw += TB_CLOCK() - w0; }
                 const uint8_t* codes = weights0 + rs * L.weight_stage;
                 const uint8_t* scales = codes + kBlockBytes;
@@ -567,7 +578,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                     }
                 }
                 [[maybe_unused]] const uint32_t w1 = TB_CLOCK();
-                if (!__all_sync(0xffffffffu, mbar_wait(br_empty(bs), bphase ^ 1u, abort_flag, kWaitBridgedEmpty))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(br_empty(bs), bphase ^ 1u, abort_flag, kWaitBridgedEmpty, 0, p.wait_cycles))) { ok = false; break; }
                 waited_empty += TB_CLOCK() - w1;
                 tc_fence_after_sync();
 #pragma unroll
@@ -606,18 +617,38 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
         // (Worked out where they are used: nothing of this stays in registers across the main loop.)
         auto wide = [&]() { return (p.n & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0; };
         auto turned_chunk = [&]() { return reinterpret_cast<__nv_bfloat16*>(smem + L.transpose + warp * kTransposeBytes); };
+        // K-split launches number themselves on the device.  Word 0 of the workspace is the sequence of the last launch
+        // that ran on it, word 1 counts the CTAs of this launch that have read it; the CTA that arrives last advances the
+        // sequence.  By then every CTA of the grid holds its copy, and the next launch on the workspace starts after this
+        // one has ended, so the tags of a launch differ from those of every earlier one -- under CUDA-graph replay and
+        // after a launch that gave up as well.  (The arrival releases, so the read before it cannot slip behind it.)
+        uint32_t launch_seq = 0;
+        if (!kGroupScales && p.layout == kDense && p.splits > 1) {
+            volatile uint32_t* const seq_slot = reinterpret_cast<volatile uint32_t*>(smem + L.misc + 8);
+            if (warp == 0 && lane == 0) {
+                unsigned* const head = reinterpret_cast<unsigned*>(p.workspace);
+                const unsigned seq = __ldcg(head) & 0x1FFFFFFu;
+                unsigned arrived;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(head + 1) : "memory");
+                if (arrived == gridDim.x - 1) {
+                    __stcg(head + 1, 0u);
+                    __stcg(head, (seq + 1u) & 0x1FFFFFFu);
+                }
+                *seq_slot = seq;
+            }
+            named_barrier_sync(1, kEpilogueWarps * 32);
+            launch_seq = *seq_slot;
+        }
         int acc = 0;
         uint32_t aphase = 0;
         bool ok = true;
         const long long route_limit = p.rows * p.top_k;
         for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
             const Unit t = decode(u);
+            if (t.skip) continue;
             const float gs = p.global_scale[t.expert];
             const bool partial = !kGroupScales && p.layout == kDense && p.splits > 1;
-            // Split-K: the tile's epoch, fetched now so that its latency hides behind the main loop.
-            unsigned* const epoch_cells = reinterpret_cast<unsigned*>(p.workspace);
-            const unsigned epoch = partial ? __ldcg(epoch_cells + t.tile) : 0u;
-            const uint32_t tag = (static_cast<uint32_t>(t.tile) << 25) | ((epoch + 1u) & 0x1FFFFFFu);
+            const uint32_t tag = (static_cast<uint32_t>(t.tile) << 25) | ((launch_seq + 1u) & 0x1FFFFFFu);
             const int cols_valid = indexed ? kCols : max(0, min(kCols, t.rows_valid - col0));  // live columns of this warp
             // Writes the turned chunk c to the staged output rows of its columns: lane -> row lane / 4 (and + 8) of the
             // chunk, 8-channel word lane % 4 of the row.
@@ -696,7 +727,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                     }
                     __syncwarp();
                     fetch(kb + 2, after);
-                    if (!mbar_wait(acc_full(acc), aphase, abort_flag, kWaitAccFull)) { ok = false; break; }
+                    if (!mbar_wait(acc_full(acc), aphase, abort_flag, kWaitAccFull, 0, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
 #pragma unroll
                     for (int c = 0; c < kCols / 32; ++c) {  // two 16-column loads in flight per wait
@@ -752,7 +783,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                     }
                 }
             } else {
-                if (!mbar_wait(acc_full(acc), aphase, abort_flag, kWaitAccFull, 100)) { ok = false; break; }
+                if (!mbar_wait(acc_full(acc), aphase, abort_flag, kWaitAccFull, 100, p.wait_cycles)) { ok = false; break; }
                 tc_fence_after_sync();
                 if (warp == 0 && lane == 0) TB_PHASE(7);
                 const int n = t.nt * 128 + n_local;
@@ -848,100 +879,103 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                         }
                     }
                 } else {
-                    // Ordered split-K reduction without counters or fences.  A split publishes the FP32 partial sums
-                    // of the columns it does not own as 8-byte {value, tag} words (single stores, so a reader sees both
-                    // halves or neither) -- all of them first, so that nobody waits on a peer that is itself waiting
-                    // -- then reads its peers' words for the columns it owns until their tags match, adds the splits in
-                    // the order 0, 1, ..., S-1 and writes the output.  The thread that holds an element in one split
-                    // holds it in all of them, so no thread waits for anything but its own elements.
-                    // Ownership: when every unit of the launch has its own CTA, all splits of a tile are resident and
-                    // share the columns evenly (from 64-token tiles up, where one SM alone would take long to read its
-                    // peers' sums); otherwise the last split owns them all -- it is the last of the tile's units in
-                    // launch order, so its peers are running or done.  Every wait is bounded.
-                    // tag = {tile, epoch of the tile + 1}: the epoch cell of a tile sits in the workspace header and is
-                    // advanced once per launch, so words left by earlier launches never match.
+                    // Ordered split-K reduction without fences.  The token columns of a tile are cut into batches of
+                    // eight and every batch has one owner among the tile's splits.  A split first publishes the FP32
+                    // partial sums of the batches it does not own as 8-byte {value, tag} words (single stores, so a
+                    // reader sees both halves or neither) -- all of them before it reads anything, so that nobody
+                    // waits on a peer that is itself waiting -- then, for each batch it owns, reads its peers' words
+                    // until their tags match, adds the splits in the order 0, 1, ..., S-1 and writes the output.  The
+                    // words of two peers are in flight at once, so three splits cost one round trip to the L2 per
+                    // batch.  The thread that holds an element in one split holds it in all of them: no thread waits
+                    // for anything but its own elements.
+                    // Ownership: when every unit of the launch has its own CTA (and so all splits of a tile are
+                    // running, or will be as soon as an SM is free), batch b belongs to split b % S; otherwise the
+                    // last split owns them all -- it is the last of the tile's units in launch order, so its peers
+                    // are running or done.  The order of the additions does not depend on the owner.  Every wait is
+                    // bounded.
+                    // tag = {tile, launch sequence + 1}: words left by earlier launches never match.
                     if (warp == 0 && lane == 0) TB_PHASE(8);
                     const int S = p.splits;
-                    const bool shared = BM >= 64 && total_units <= static_cast<int>(gridDim.x);
-                    const int own_lo = shared ? t.split * cols_valid / S : (t.split == S - 1 ? 0 : cols_valid);
-                    const int own_hi = shared ? (t.split + 1) * cols_valid / S : cols_valid;
+                    const bool shared = total_units <= static_cast<int>(gridDim.x);
                     uint2* const slots = reinterpret_cast<uint2*>(p.workspace + kEpochCells) +
                                          static_cast<long long>(t.tile) * S * (BM * 128) + col0 * 128 + n_local;
-                    for (int c = 0; c < kCols / 16; ++c) {  // pass 1: publish
-                        if (c * 16 >= cols_valid) break;
-                        if (c * 16 >= own_lo && c * 16 + 16 <= own_hi) continue;  // all mine
-                        uint32_t v[16];
-                        tmem_ld_16(lane_base + acc * BM + col0 + c * 16, v);
+                    const int batches = (cols_valid + 7) >> 3;
+                    const int first_batch = col0 >> 3;  // index of this warp's first batch within the tile
+                    for (int b = 0; b < batches; ++b) {  // pass 1: publish
+                        if ((shared ? (first_batch + b) % S : S - 1) == t.split) continue;
+                        uint32_t v[8];
+                        tmem_ld_8(lane_base + acc * BM + col0 + b * 8, v);
                         tmem_ld_wait();
-                        uint2* out = slots + (t.split * BM + c * 16) * 128;
+                        uint2* out = slots + (t.split * BM + b * 8) * 128;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int i = c * 16 + j;
-                            if (i < cols_valid && (i < own_lo || i >= own_hi))
+                        for (int j = 0; j < 8; ++j) {
+                            if (b * 8 + j < cols_valid)
                                 asm volatile("st.global.cg.v2.b32 [%0], {%1, %2};" ::"l"(out + j * 128), "r"(v[j]), "r"(tag) : "memory");
                         }
                     }
-                    for (int c = 0; c < kCols / 16 && ok; ++c) {  // pass 2: reduce the owned columns
-                        if (c * 16 >= own_hi) break;
-                        if (c * 16 + 16 <= own_lo) continue;
-                        uint32_t v[16];
-                        tmem_ld_16(lane_base + acc * BM + col0 + c * 16, v);
-                        tmem_ld_wait();
+                    for (int b = 0; b < batches && ok; ++b) {  // pass 2: reduce the owned batches
+                        if ((shared ? (first_batch + b) % S : S - 1) != t.split) continue;
+                        const int live = min(8, cols_valid - b * 8);
+                        const uint32_t want = (1u << live) - 1u;
+                        float sum[8];
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {  // eight columns at a time keep the words in flight within 16 registers
-                            const int first = c * 16 + h * 8;
-                            uint32_t want = 0;
+                        for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+                        // Every lane runs every step (the tensor-memory load of the own partial sums is warp-wide); a lane
+                        // whose wait ran out stops polling and its warp leaves after the batch.
+                        for (int sp = 0; sp < S; sp += 2) {  // splits sp and sp + 1, fixed order of additions
+                            uint2 got[2][8];
+                            uint32_t need0 = (ok && sp != t.split) ? want : 0u;
+                            uint32_t need1 = (ok && sp + 1 < S && sp + 1 != t.split) ? want : 0u;
+                            const uint2* in = slots + (sp * BM + b * 8) * 128;
+                            long long start = 0;
+                            for (uint32_t spin = 0; (need0 | need1) != 0u; ++spin) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) want |= (first + j >= own_lo && first + j < own_hi) ? 1u << j : 0u;
-                            if (want == 0) continue;
-                            float sum[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) sum[j] = 0.f;
-                            for (int sp = 0; sp < S && ok; ++sp) {  // fixed order: split 0 first
-                                if (sp == t.split) {
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(v[h * 8 + j]);
-                                    continue;
-                                }
-                                const uint2* in = slots + (sp * BM + first) * 128;
-                                uint2 got[8];
-                                uint32_t ready = 0;
-                                long long start = 0;
-                                for (uint32_t spin = 0; ready != want; ++spin) {
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        if (((want & ~ready) >> j) & 1u)
-                                            asm volatile("ld.global.cg.v2.b32 {%0, %1}, [%2];" : "=r"(got[j].x), "=r"(got[j].y) : "l"(in + j * 128) : "memory");
-                                    }
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        if ((((want & ~ready) >> j) & 1u) && got[j].y == tag) ready |= 1u << j;
-                                    }
-                                    if (ready == want) break;
-                                    if (spin == 0) {
-                                        start = clock64();
-                                    } else if ((spin & 15u) == 0u && (*abort_flag != 0 || clock64() - start > kWaitCycles)) {
-                                        atomicCAS(const_cast<int*>(abort_flag), 0, kWaitSplit);
-                                        ok = false;
-                                        break;
-                                    }
+                                for (int j = 0; j < 8; ++j) {
+                                    if ((need0 >> j) & 1u)
+                                        asm volatile("ld.global.cg.v2.b32 {%0, %1}, [%2];" : "=r"(got[0][j].x), "=r"(got[0][j].y)
+                                                     : "l"(in + j * 128) : "memory");
+                                    if ((need1 >> j) & 1u)
+                                        asm volatile("ld.global.cg.v2.b32 {%0, %1}, [%2];" : "=r"(got[1][j].x), "=r"(got[1][j].y)
+                                                     : "l"(in + (BM + j) * 128) : "memory");
                                 }
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) {
-                                    if ((want >> j) & 1u) sum[j] += __uint_as_float(got[j].x);
+                                    if (((need0 >> j) & 1u) && got[0][j].y == tag) need0 &= ~(1u << j);
+                                    if (((need1 >> j) & 1u) && got[1][j].y == tag) need1 &= ~(1u << j);
+                                }
+                                if ((need0 | need1) == 0u) break;
+                                if (spin == 0) {
+                                    start = clock64();
+                                } else if ((spin & 15u) == 0u && (*abort_flag != 0 || clock64() - start > p.wait_cycles)) {
+                                    atomicCAS(const_cast<int*>(abort_flag), 0, kWaitSplit);
+                                    ok = false;
+                                    break;
                                 }
                             }
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int i = first + j;
-                                if (((want >> j) & 1u) && n_ok && ok)
-                                    p.d[static_cast<long long>(my_row[i]) * p.n + n] = __float2bfloat16_rn(sum[j] * my_scale[i]);
+                            for (int q = 0; q < 2; ++q) {
+                                if (sp + q >= S) break;
+                                if (sp + q == t.split) {  // warp-uniform
+                                    uint32_t v[8];
+                                    tmem_ld_8(lane_base + acc * BM + col0 + b * 8, v);
+                                    tmem_ld_wait();
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(v[j]);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) sum[j] += __uint_as_float(got[q][j].x);
+                                }
                             }
                         }
+                        ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int i = b * 8 + j;
+                            if (((want >> j) & 1u) && n_ok && ok)
+                                p.d[static_cast<long long>(my_row[i]) * p.n + n] = __float2bfloat16_rn(sum[j] * my_scale[i]);
+                        }
                     }
-                    const bool reducer = t.split == S - 1;
-                    if (reducer && warp == 0 && lane == 0) epoch_cells[t.tile] = epoch + 1;
-                    if (warp == 0 && lane == 0) TB_PHASE(reducer ? 9 : 10);
+                    if (warp == 0 && lane == 0) TB_PHASE(t.split == S - 1 ? 9 : 10);
                 }
                 tc_fence_before_sync();
                 __syncwarp();

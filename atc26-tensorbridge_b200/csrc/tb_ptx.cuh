@@ -46,15 +46,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Cycle budget of one wait: about a second at the B200's clocks.
+// Default cycle budget of one wait: about a second at the B200's clocks.
 constexpr long long kWaitCycles = 1ll << 31;
 
-// Waits for the phase with `parity` of `bar` to complete.  Returns false when the budget runs out or another
+// Waits for the phase with `parity` of `bar` to complete.  Returns false when `budget` cycles run out or another
 // thread of the CTA has already given up (`*abort_flag != 0`); the first thread to give up stores `code`.
 // `sleep_ns` > 0 backs off between polls: for waits that last a whole main loop, so that the polling warps stay out of
 // the way of the warps doing the work (they share the issue slots and the shared-memory pipe).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          unsigned sleep_ns = 0) {
+                                          unsigned sleep_ns = 0, long long budget = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (uint32_t spin = 1;; ++spin) {
@@ -62,7 +62,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (sleep_ns != 0) __nanosleep(sleep_ns);
         if ((spin & 63u) == 0u) {
             if (*abort_flag != 0) return false;
-            if (clock64() - start > kWaitCycles) {
+            if (clock64() - start > budget) {
                 atomicCAS(const_cast<int*>(abort_flag), 0, code);
                 return false;
             }
@@ -188,6 +188,13 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// The same for 8 consecutive columns.
+__device__ __forceinline__ void tmem_ld_8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 // 8 registers per thread -> 8 consecutive 32-bit columns of this thread's lane (lane = 32 * (warp % 4) + thread lane).
 __device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint4& a, const uint4& b) {

@@ -44,6 +44,7 @@ class GemmArgs(ctypes.Structure):
         ("workspace_bytes", ctypes.c_int64), ("d", ctypes.c_void_p), ("rows", ctypes.c_int64), ("n", ctypes.c_int64),
         ("k", ctypes.c_int64), ("bridge", ctypes.c_int32), ("group_scales", ctypes.c_int32),
         ("enable_pdl", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("status", ctypes.c_void_p),
+        ("wait_us", ctypes.c_int32), ("only_split", ctypes.c_int32),
     ]
 
 
@@ -138,6 +139,8 @@ def ptr(tensor: torch.Tensor | None) -> int | None:
 
 # Per-device status words the GEMM kernels write when a bounded wait gives up.
 _status: dict[int, torch.Tensor] = {}
+# Called with the device index when check_status() finds an error (the GEMM module zeroes its split-K scratch there).
+error_hooks: list = []
 
 
 def status_words(device: int) -> torch.Tensor:
@@ -156,4 +159,6 @@ def check_status(device: int | None = None) -> None:
     host = words.tolist()
     if host[0] != 0:
         words.zero_()
+        for hook in error_hooks:
+            hook(device)
         raise RuntimeError(f"tensorbridge kernel gave up waiting (site {host[0]}, block {host[1]}, units {host[2]})")

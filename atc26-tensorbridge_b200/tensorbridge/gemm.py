@@ -46,20 +46,37 @@ Routing = IndexedRouting | ContiguousRouting | MaskedRouting
 
 # FP32 split-K scratch per (device, stream): distinct streams never share partial sums.
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# Buffers that were replaced by larger ones.  A CUDA graph captured earlier on the stream still launches with the old
+# pointer, so the old buffer must stay allocated for as long as the process may replay that graph: buffers only ever
+# grow by appending, nothing is handed back to the allocator.
+_retired: list[torch.Tensor] = []
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
-    """A scratch buffer of at least `nbytes` for the current stream, or None when one would have to be allocated
-    while the stream is being captured into a CUDA graph."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+def _workspace(device: torch.device, nbytes: int, stream: int) -> torch.Tensor | None:
+    """A scratch buffer of at least `nbytes` for `stream`, or None when one would have to be allocated while the
+    stream is being captured into a CUDA graph."""
+    key = (device.index, stream)
     have = _workspaces.get(key)
     if have is not None and have.numel() * 4 >= nbytes:
         return have
     if torch.cuda.is_current_stream_capturing():
         return None
-    # zeros: the head of the buffer holds the per-tile epochs the tagged split-K partial sums are matched against
+    if have is not None:
+        _retired.append(have)
+    # zeros: the head of the buffer holds the launch sequence the tagged split-K partial sums are matched against
     _workspaces[key] = torch.zeros(max(nbytes, 8 << 20) // 4, dtype=torch.float32, device=device)
     return _workspaces[key]
+
+
+def reset_workspaces(device: int | None = None) -> None:
+    """Zero the split-K scratch of `device` (all devices when None).  Needed only after `check_status()` reported a
+    kernel that gave up waiting, if the same CUDA graph is to be replayed: eager launches number themselves afresh."""
+    for (index, _), buffer in _workspaces.items():
+        if device is None or index == device:
+            buffer.zero_()
+
+
+_native.error_hooks.append(reset_workspaces)
 
 
 # Indexed launches first gather their routed rows into scratch (then the GEMM loads tiles by TMA); set to False to let
@@ -79,6 +96,8 @@ def _gather_buffer(device: torch.device, nbytes: int) -> torch.Tensor | None:
         return have
     if torch.cuda.is_current_stream_capturing():
         return None
+    if have is not None:
+        _retired.append(have)
     _gather_buffers[key] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
     return _gather_buffers[key]
 
@@ -124,29 +143,62 @@ def _output(out: torch.Tensor | None, rows: int, n: int, like: torch.Tensor) -> 
 PDL_STATIC_WEIGHTS = 2
 
 
+class _Call:
+    """The argument structs of one (weight, shape, config, launch mode): built once, patched per call."""
+
+    __slots__ = ("args", "cfg", "routing", "args_ref", "cfg_ref", "routing_ref", "need", "unsplit_cfg_ref", "unsplit_cfg")
+
+    def __init__(self, args, cfg, routing, need):
+        self.args, self.cfg, self.routing, self.need = args, cfg, routing, need
+        self.args_ref, self.cfg_ref = ctypes.byref(args), ctypes.byref(cfg)
+        self.routing_ref = None if routing is None else ctypes.byref(routing)
+        self.unsplit_cfg = self.unsplit_cfg_ref = None
+        if need > 0:
+            self.unsplit_cfg = _native.Config.from_buffer_copy(cfg)
+            self.unsplit_cfg.use_stream_k = 0
+            self.unsplit_cfg_ref = ctypes.byref(self.unsplit_cfg)
+
+
+_dense_calls: dict[tuple, _Call] = {}
+
+
 def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, rows, n, k, bridge, group_scales,
-            enable_pdl, config, routing_struct):
+            enable_pdl, config, routing_struct, call: _Call | None = None) -> _Call:
+    """One launch through the C ABI.  `call` carries the structs of an earlier launch with the same weight, shape,
+    config and mode: only the activation, scale, output, workspace and status pointers are patched."""
     device = a.device
     lib = _native.load()
-    cfg = _config_struct(config)
-    workspace = None
-    need = lib.tb_workspace_bytes(rows, n, ctypes.byref(cfg)) if routing_struct is None else 0
-    if need > 0:
-        workspace = _workspace(device, need)
+    if call is None:
+        cfg = _config_struct(config)
+        need = lib.tb_workspace_bytes(rows, n, ctypes.byref(cfg)) if routing_struct is None else 0
+        args = _native.GemmArgs(
+            0, 0, strides[0], strides[1], weight_t.data_ptr(), scale_t.data_ptr(), global_scale.data_ptr(),
+            locks.data_ptr(), None, 0, 0, rows, n, k, _native.BRIDGE_IDS[bridge], int(group_scales), int(enable_pdl), 0,
+            _native.status_words(device.index).data_ptr())
+        call = _Call(args, cfg, routing_struct, need)
+    args = call.args
+    args.a, args.a_scale, args.d = a.data_ptr(), a_scale.data_ptr(), out.data_ptr()
+    args.a_scale_stride_m, args.a_scale_stride_k = strides
+    current = torch.cuda.current_device() == device.index
+    stream = torch.cuda.current_stream(device).cuda_stream
+    cfg_ref = call.cfg_ref
+    if call.need > 0:
+        workspace = _workspace(device, call.need, stream)
         if workspace is None:  # capturing without a buffer: run unsplit rather than allocate inside the capture
-            cfg.use_stream_k = 0
-            need = 0
-    args = _native.GemmArgs(
-        a.data_ptr(), a_scale.data_ptr(), strides[0], strides[1], weight_t.data_ptr(), scale_t.data_ptr(),
-        global_scale.data_ptr(), locks.data_ptr(), _native.ptr(workspace),
-        0 if workspace is None else workspace.numel() * 4, out.data_ptr(), rows, n, k, _native.BRIDGE_IDS[bridge],
-        int(group_scales), int(enable_pdl), 0, _native.status_words(device.index).data_ptr())
-    with torch.cuda.device(device):
-        stream = _native.stream_ptr(device)
-        if routing_struct is None:
-            _native.check(lib.tb_gemm_dense(stream, ctypes.byref(args), ctypes.byref(cfg)))
+            cfg_ref = call.unsplit_cfg_ref
+            args.workspace, args.workspace_bytes = None, 0
         else:
-            _native.check(lib.tb_gemm_grouped(stream, ctypes.byref(args), ctypes.byref(routing_struct), ctypes.byref(cfg)))
+            args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
+    if current:
+        code = (lib.tb_gemm_dense(stream, call.args_ref, cfg_ref) if call.routing is None else
+                lib.tb_gemm_grouped(stream, call.args_ref, call.routing_ref, cfg_ref))
+    else:
+        with torch.cuda.device(device):
+            code = (lib.tb_gemm_dense(stream, call.args_ref, cfg_ref) if call.routing is None else
+                    lib.tb_gemm_grouped(stream, call.args_ref, call.routing_ref, cfg_ref))
+    if code:
+        _native.check(code)
+    return call
 
 
 def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, out: torch.Tensor | None = None,
@@ -165,22 +217,28 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
     """
     n, k = weight.shape
     strides = _check_common(a, a_scale, k, group_scales)
-    n_pad, k_pad = pad_to_unit(n), pad_to_unit(k)
-    _require(weight.weight.dtype == torch.int32 and tuple(weight.weight.shape) == (n_pad, k_pad // 8)
-             and weight.weight.is_contiguous(), f"weight.weight must be contiguous int32 [{n_pad}, {k_pad // 8}]")
-    want_scale = (k_pad // 128, n_pad, 8) if group_scales else (k_pad // 16, n_pad)
-    _require(tuple(weight.scale.shape) == want_scale and weight.scale.is_contiguous(),
-             f"weight.scale must be contiguous {want_scale}")
-    _require(weight.global_scale.numel() == 1 and weight.global_scale.dtype == torch.float32, "global_scale must be FP32 [1]")
-    _require(weight.locks.dtype == torch.int32 and weight.locks.numel() >= 1024, "locks must be int32 [1024]")
     m = a.size(0)
     d = _output(out, m, n, a)
     if m == 0:
         return d
     if config is None:
         config = runtime.select_config(m, n, k, device=a.get_device(), bridge=weight.bridge, group_scales=group_scales)
-    _launch(a, a_scale, strides, weight.weight, weight.scale, weight.global_scale, weight.locks, d, m, n, k,
-            weight.bridge, group_scales, enable_pdl, config, None)
+    key = (weight.weight.data_ptr(), weight.scale.data_ptr(), weight.global_scale.data_ptr(), weight.locks.data_ptr(), m, n, k,
+           weight.bridge, group_scales, int(enable_pdl), config, a.get_device())
+    call = _dense_calls.get(key)
+    if call is None:
+        n_pad, k_pad = pad_to_unit(n), pad_to_unit(k)
+        _require(weight.weight.dtype == torch.int32 and tuple(weight.weight.shape) == (n_pad, k_pad // 8)
+                 and weight.weight.is_contiguous(), f"weight.weight must be contiguous int32 [{n_pad}, {k_pad // 8}]")
+        want_scale = (k_pad // 128, n_pad, 8) if group_scales else (k_pad // 16, n_pad)
+        _require(tuple(weight.scale.shape) == want_scale and weight.scale.is_contiguous(),
+                 f"weight.scale must be contiguous {want_scale}")
+        _require(weight.global_scale.numel() == 1 and weight.global_scale.dtype == torch.float32, "global_scale must be FP32 [1]")
+        _require(weight.locks.dtype == torch.int32 and weight.locks.numel() >= 1024, "locks must be int32 [1024]")
+        if len(_dense_calls) > 4096:
+            _dense_calls.clear()
+    _dense_calls[key] = _launch(a, a_scale, strides, weight.weight, weight.scale, weight.global_scale, weight.locks, d, m, n,
+                                k, weight.bridge, group_scales, enable_pdl, config, None, call)
     return d
 
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 
 import torch
 
@@ -19,12 +20,20 @@ SelectionKey = tuple
 selected_configs: dict[SelectionKey, GemmConfig] = {}
 
 
+_num_sms: dict[tuple[int, str | None], int] = {}
+
+
 def get_num_sms(device: int | None = None) -> int:
-    """SMs available to a launch on `device`, after the `TENSORBRIDGE_NUM_SMS` cap."""
+    """SMs available to a launch on `device`, after the `TENSORBRIDGE_NUM_SMS` cap (looked up once per device and
+    value of that variable)."""
     device = torch.cuda.current_device() if device is None else device
-    out = ctypes.c_int(0)
-    _native.check(_native.load().tb_num_sms(int(device), ctypes.byref(out)))
-    return out.value
+    key = (device, os.environ.get("TENSORBRIDGE_NUM_SMS"))
+    hit = _num_sms.get(key)
+    if hit is None:
+        out = ctypes.c_int(0)
+        _native.check(_native.load().tb_num_sms(int(device), ctypes.byref(out)))
+        hit = _num_sms[key] = out.value
+    return hit
 
 
 @functools.cache

@@ -90,8 +90,8 @@ int tb_num_sms(int device, int* num_sms);
  * tensorbridge/csrc/heuristics/sm90_rule.hpp:333-348. */
 int tb_select_config(const tb_problem* problem, tb_config* config);
 
-/* Bytes of scratch a dense launch with `config` needs for its K splits (0 without splits): 4 KB of tile epochs and
- * one 8-byte {partial sum, tag} word per element of every split.
+/* Bytes of scratch a dense launch with `config` needs for its K splits (0 without splits, or for a block_m the
+ * library does not have): a 4 KB header and one 8-byte {partial sum, tag} word per element of every split.
  * No counterpart in the reference, whose Stream-K tail adds into the BF16 output in place. */
 int64_t tb_workspace_bytes(int64_t m, int64_t n, const tb_config* config);
 
@@ -174,8 +174,9 @@ typedef struct tb_gemm_args {
                              * (the K-split reduction needs no counters), may be NULL */
     float* workspace;       /* scratch of tb_workspace_bytes() for K splits, 8-byte aligned, or NULL when the config has
                              * none.  Zero it once after allocating it and leave its first 4 KB alone afterwards: they
-                             * hold the per-tile epochs that tell this launch's partial sums from older ones.  Launches
-                             * that can overlap need separate workspaces. */
+                             * hold the launch sequence number that tells this launch's partial sums from older ones
+                             * (kept on the device, so CUDA-graph replays number themselves too).  Launches that can
+                             * overlap need separate workspaces. */
     int64_t workspace_bytes;
     void* d;                /* BF16 [out_rows, n] contiguous */
     int64_t rows;           /* rows of `a` */
@@ -188,6 +189,10 @@ typedef struct tb_gemm_args {
                              * stream them before the previous kernel has finished */
     int32_t num_sms;        /* 0 = all SMs of the device (after TENSORBRIDGE_NUM_SMS) */
     int32_t* status;        /* device int32 [4] the kernel writes on a timed-out wait, or NULL */
+    int32_t wait_us;        /* budget of every wait inside the kernel in microseconds (counted at 2 GHz); 0 = about a
+                             * second.  A wait that runs out makes the kernel return early and write `status`. */
+    int32_t only_split;     /* test hook, dense K splits only: s + 1 runs just the units of split s, so that its peers'
+                             * partial sums never arrive and its bounded wait runs out; 0 = all units (normal use) */
 } tb_gemm_args;
 
 /* D[m, n] = bf16((A @ bridge(W).T) * a_scale * global_scale).
@@ -201,11 +206,12 @@ int tb_gemm_dense(void* stream, const tb_gemm_args* args, const tb_config* confi
  * synchronise the device -- and that still want the K-split kernel for small M.  This function and everything it
  * calls performs no cudaMalloc, cudaFree or other allocating call.
  *   - A launch whose K splits need more than 8 MiB (tb_workspace_bytes(rows, n, config) > 8 << 20) is rejected with
- *     TB_ERR_INVALID and a message that states both sizes; configs without a K split need no scratch and always pass.
+ *     TB_ERR_INVALID and a message that states both sizes.  The size is that of the splits the launch really makes
+ *     (at most one per 128 of K, none with [1,128] scales): launches without a K split need no scratch and always pass.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current).  Make that first call outside any CUDA stream capture; later calls only launch.
  *   - All calls on a device share the one array and it keeps whatever the last launch left there: it starts zeroed
- *     (static storage), its first 4 KB hold the tile epochs and every partial sum carries the tag of its launch.  Two
+ *     (static storage), its first 4 KB hold the launch sequence number and every partial sum carries the tag of its launch.  Two
  *     launches that may run at the same time on one device (different streams) would overwrite each other's partial
  *     sums: serialise them, or use tb_gemm_dense with one workspace per stream.
  * The inputs, the output and `status` are still the caller's, exactly as for tb_gemm_dense.

@@ -31,7 +31,7 @@ def test_struct_sizes_match_header(lib):
     from tensorbridge import _native
     assert ctypes.sizeof(_native.Config) == 36
     assert ctypes.sizeof(_native.Problem) == 48
-    assert ctypes.sizeof(_native.GemmArgs) == 17 * 8
+    assert ctypes.sizeof(_native.GemmArgs) == 18 * 8  # 17 eight-byte slots + wait_us, only_split
     assert ctypes.sizeof(_native.Routing) == 8 + 5 * 8 + 8 + 8 + 16
 
 
@@ -59,6 +59,39 @@ def test_workspace_bytes(lib):
     assert lib.tb_workspace_bytes(16, 6144, ctypes.byref(cfg)) == 4096 + 48 * 3 * 16 * 128 * 8
     cfg.use_stream_k = 0
     assert lib.tb_workspace_bytes(16, 6144, ctypes.byref(cfg)) == 0
+    # a token tile the library does not have is answered with 0, not a division by zero
+    for bad in (0, 24, -16):
+        cfg = _native.Config(bad, 8, 3, 0, 128, 128, 1, 3, 2)
+        assert lib.tb_workspace_bytes(16, 6144, ctypes.byref(cfg)) == 0
+
+
+def test_static_scratch_entry_validates_before_sizing(lib):
+    """The allocation-free entry point refuses an unknown token tile with an error code, and sizes its scratch by the
+    splits the launch really makes: more splits than K blocks, or [1,128] scales, need little or none and are not
+    refused for size (they fail later, on the null tensors, with the ordinary message)."""
+    from tensorbridge import _native
+    args = _native.GemmArgs()
+    args.rows, args.n, args.k = 256, 2048, 256
+    cfg = _native.Config(0, 4, 8, 2, 128, 128, 1, 3, 2)
+    assert lib.tb_gemm_dense_static_scratch(None, ctypes.byref(args), ctypes.byref(cfg)) == _native.ERR_INVALID
+    assert b"block_m" in lib.tb_last_error()
+    # 16 tiles x 16 splits x 256 x 128 x 8 B = 64 MiB by the config, but K = 256 allows only two splits: 8 MiB + header
+    cfg = _native.Config(256, 4, 16, 2, 128, 128, 1, 3, 2)
+    args.rows, args.n = 256, 1024  # 8 tiles x 2 splits x 256 x 128 x 8 B = 4 MiB
+    assert lib.tb_workspace_bytes(256, 1024, ctypes.byref(cfg)) > 8 << 20
+    # past the size check the call goes on to the device (no GPU here: a CUDA error) or to the null tensors
+    assert lib.tb_gemm_dense_static_scratch(None, ctypes.byref(args), ctypes.byref(cfg)) != _native.OK
+    assert b"split-K scratch" not in lib.tb_last_error()
+    args.group_scales = 1
+    args.rows, args.n = 256, 2048
+    assert lib.tb_gemm_dense_static_scratch(None, ctypes.byref(args), ctypes.byref(cfg)) != _native.OK
+    assert b"split-K scratch" not in lib.tb_last_error()
+    args.group_scales = 0  # and the same shape with per-token scales is refused for its size
+    cfg.use_stream_k = 2
+    args.k = 1024
+    args.rows, args.n = 512, 2048  # 32 tiles x 2 splits x 256 x 128 x 8 B = 16 MiB
+    assert lib.tb_gemm_dense_static_scratch(None, ctypes.byref(args), ctypes.byref(cfg)) == _native.ERR_INVALID
+    assert b"split-K scratch" in lib.tb_last_error()
 
 
 def test_validation_needs_no_gpu(lib):

@@ -100,6 +100,48 @@ def test_dense_split_k_is_deterministic_and_correct(splits, block_m):
     assert int(weight.locks.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("num_sms", [0, 1])
+def test_split_k_wait_runs_out_reports_and_recovers(num_sms):
+    """A bounded wait that runs out ends the launch with a status code instead of a hang.  Made to happen from the host:
+    only the last of a tile's two K splits is launched (`only_split`), with a 2 ms budget, so the partial sums it waits
+    for never arrive.  The kernel must return, report the split-K wait site, leave the output alone, and the next
+    ordinary launch on the same workspace must be right -- with all CTAs resident (the splits share the columns) and
+    on one SM (the last split reduces)."""
+    import ctypes
+    import tensorbridge as tb
+    from tensorbridge import _native as native
+    lib = native.load()
+    m, n, k = 13, 256, 1792
+    view, weight, q, s, wq, ws = _case(m, n, k, "exact", seed=5)
+    config = native.Config(16, 4, 2, 2, 128, 128, 1, 4, 2)
+    need = lib.tb_workspace_bytes(m, n, ctypes.byref(config))
+    workspace = torch.zeros(need // 4, dtype=torch.float32, device="cuda")
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    tb.check_status()
+
+    def args(only_split, wait_us):
+        return native.GemmArgs(q.data_ptr(), s.data_ptr(), 1, 0, weight.weight.data_ptr(), weight.scale.data_ptr(),
+                               weight.global_scale.data_ptr(), weight.locks.data_ptr(), workspace.data_ptr(), need,
+                               out.data_ptr(), m, n, k, native.BRIDGE_IDS["exact"], 0, 0, num_sms,
+                               native.status_words(0).data_ptr(), wait_us, only_split)
+
+    stream = torch.cuda.current_stream().cuda_stream
+    a = args(only_split=2, wait_us=2000)
+    native.check(lib.tb_gemm_dense(stream, ctypes.byref(a), ctypes.byref(config)))
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match=f"site {9}"):
+        tb.check_status()
+    assert bool((out == 7.0).all())  # the waiting split wrote nothing, the other never ran
+    tb.check_status()  # the status words were cleared by the failing check
+    for _ in range(2):  # the same workspace, not zeroed: this launch numbers itself past the one that gave up
+        a = args(only_split=0, wait_us=0)
+        native.check(lib.tb_gemm_dense(stream, ctypes.byref(a), ctypes.byref(config)))
+        torch.cuda.synchronize()
+        tb.check_status()
+        _check(out, view, wq, ws, n, k)
+        out.fill_(7.0)
+
+
 @pytest.mark.parametrize("bridge_warps", [(2, 2), (4, 4)])
 @pytest.mark.parametrize("m,block_m,splits", [(200, 64, 3), (200, 128, 3), (131, 192, 2), (200, 192, 3), (250, 256, 5), (7, 64, 4)])
 def test_dense_split_k_shared_reduction(m, block_m, splits, bridge_warps):

@@ -49,6 +49,7 @@ def _all_code_scale_pairs():
 def test_closed_form_equals_device_table_lookup(bridge):
     codes, raw = _all_code_scale_pairs()
     assert np.array_equal(orc.bridge_bytes(codes, raw, bridge), orc.bridge_bytes_lut(codes, raw, bridge))
+    assert np.array_equal(orc.bridge_bytes(codes, raw, bridge), orc.bridge_bytes_by_table(codes, raw, bridge))
 
 
 def test_exact_bridge_is_rne_of_code_times_scale_over_six():
@@ -156,3 +157,4 @@ def test_table_dequant_equals_closed_form():
         v = orc.prepare_reference_view(p, sc, gs, bridge=bridge)
         fast = orc.dequant_weight_f32(v["codes"], v["raw"], bridge).numpy()
         assert np.array_equal(fast, orc.e4m3_decode(v["fp8"]))
+        assert np.array_equal(v["fp8"], orc.bridge_bytes(v["codes"], v["raw"], bridge))  # the view's gather == closed form
