@@ -339,6 +339,7 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
         return fail(TB_ERR_INVALID, "config needs %zu bytes of shared memory, the device offers %d", smem, info.smem_optin);
 
     p.splits = 1;
+    p.div_n_tiles = tb::FastDiv::make(static_cast<uint32_t>(p.n_tiles));
     p.m_blocks = ceil_div(a->rows, bm);
     long long units;
     if (layout == TB_LAYOUT_DENSE) {
@@ -410,6 +411,7 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
             return rc;
     }
 
+    p.div_splits = tb::FastDiv::make(static_cast<uint32_t>(p.splits));
     const int grid = static_cast<int>(std::min<long long>(units, sms));
     const bool exact = a->bridge == TB_BRIDGE_EXACT;
     if (a->bridge != TB_BRIDGE_EXACT && a->bridge != TB_BRIDGE_FPMA) return fail(TB_ERR_INVALID, "unknown bridge %d", a->bridge);

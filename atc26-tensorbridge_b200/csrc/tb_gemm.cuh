@@ -62,6 +62,28 @@ enum WaitCode : int {
     kWaitAccFull = 7, kWaitTokenFull = 8, kWaitSplit = 9
 };
 
+// Division of a non-negative int below 2^31 by an invariant positive divisor: one multiply-high and a shift, with the
+// two constants worked out on the host.  The unit decode runs at the head of every role's serial instruction stream
+// (a single thread issues one dependent instruction every few cycles), where five hardware-emulated divisions cost
+// half a microsecond of a ten-microsecond launch.
+struct FastDiv {
+    uint32_t mul, shr, divisor, pad;
+    __host__ static FastDiv make(uint32_t d) {
+        FastDiv f = {0, 0, d, 0};
+        if (d > 1) {
+            uint32_t log2_ceil = 0;
+            while ((1ull << log2_ceil) < d) ++log2_ceil;
+            const uint32_t bits = 31 + log2_ceil;
+            f.mul = static_cast<uint32_t>(((1ull << bits) + d - 1) / d);
+            f.shr = bits - 32;
+        }
+        return f;
+    }
+    __device__ __forceinline__ int div(int n) const {
+        return divisor == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
+    }
+};
+
 struct alignas(64) GemmParams {
     CUtensorMap map_a;   // activations uint8 [rows, k]: box 128 x BM, 128-byte swizzle (unused for indexed)
     CUtensorMap map_sf;  // scales uint8 [E * k_pad/16, n_pad]: box 128 x 8 (unused with group scales)
@@ -91,6 +113,7 @@ struct alignas(64) GemmParams {
     const int* num_tokens_padded;
     long long sorted_capacity;
     int* status;
+    FastDiv div_splits, div_n_tiles;  // dense unit -> (tile, split); tile or token block -> (token block, channel tile)
     long long wait_cycles;  // budget of every bounded wait
     int only_split;         // test hook: s + 1 runs only the units of K split s (0 = all)
 };
@@ -211,9 +234,10 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
     const bool gather = indexed && p.a_gathered == 0;  // rows fetched one by one inside the kernel
 
     // ---- set-up (overlaps the previous kernel under PDL: no global reads yet) ----
-    if (threadIdx.x == 0) { *abort_flag = 0; TB_PHASE(0); }
+    if (threadIdx.x == 0) TB_PHASE(0);
     if (warp == kWeightWarp) {
         if (lane == 0) {
+            *abort_flag = 0;  // by the warp that does not wait at the set-up barrier, so that it never reads it unset
             prefetch_tensormap(&p.map_a);
             prefetch_tensormap(&p.map_sf);
         }
@@ -236,10 +260,17 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
         tmem_alloc(base_u32 + L.misc, tmem_cols);
         tmem_relinquish();
     }
+    // The weight producer needs nothing of what the other warps set up (it made the barriers itself): it arrives at
+    // the CTA barrier without waiting, so that its first copies are on their way while the tensor memory is still
+    // being allocated.  (A barrier of its own: the one at the end of the kernel is the plain CTA barrier.)
     tc_fence_before_sync();
-    __syncthreads();
+    if (warp == kWeightWarp) {
+        asm volatile("barrier.arrive 2, %0;" ::"r"(static_cast<uint32_t>(blockDim.x)) : "memory");
+    } else {
+        asm volatile("barrier.sync 2, %0;" ::"r"(static_cast<uint32_t>(blockDim.x)) : "memory");
+    }
     tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = warp == kWeightWarp ? 0u : *tmem_slot;
 
     // Let a kernel launched behind this one with programmatic dependent launch start its own set-up now: it waits for
     // this whole grid (griddepcontrol.wait) before it reads anything, so releasing it early costs nothing.
@@ -310,19 +341,18 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
         t.kb1 = p.k_blocks;
         t.expert = 0;
         if (p.layout == kDense) {
-            t.split = u % p.splits;
-            t.tile = u / p.splits;
-            const int g = t.tile / n_groups;
+            t.tile = p.div_splits.div(u);
+            t.split = u - t.tile * p.splits;
+            const int g = p.div_n_tiles.div(t.tile);
             t.nt = t.tile - g * n_groups;
             t.row0 = g * BM;
             t.rows_valid = min(BM, static_cast<int>(p.rows) - t.row0);
-            // 32-bit on purpose (at most 16 splits of fewer than 2^27 blocks): a 64-bit division costs about a microsecond
-            // of set-up per unit.
-            t.kb0 = static_cast<int>(static_cast<unsigned>(t.split) * static_cast<unsigned>(p.k_blocks) / static_cast<unsigned>(p.splits));
-            t.kb1 = static_cast<int>(static_cast<unsigned>(t.split + 1) * static_cast<unsigned>(p.k_blocks) / static_cast<unsigned>(p.splits));
+            // at most 16 splits of fewer than 2^27 blocks: the products stay below 2^31
+            t.kb0 = p.div_splits.div(t.split * p.k_blocks);
+            t.kb1 = p.div_splits.div((t.split + 1) * p.k_blocks);
             t.skip = p.only_split != 0 && t.split != p.only_split - 1;
         } else {
-            const int g = u / n_groups;
+            const int g = p.div_n_tiles.div(u);
             t.nt = u - g * n_groups;
             t.tile = u;
             if (indexed) {
@@ -364,6 +394,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
                 const Unit t = decode(u);
                 if (t.skip) continue;
+                if (u == static_cast<int>(blockIdx.x)) TB_PHASE(14);
                 const uint8_t* codes =
                     p.weight + ((static_cast<long long>(t.expert) * p.n_tiles + t.nt) * p.k_blocks + t.kb0) * kBlockBytes;
                 // group scales: [E, K/128, n_pad, 8] bytes, 1 KB per (K block, channel tile); else a TMA box of the
@@ -376,6 +407,7 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
                     [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
                     if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitWeightEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     waited += TB_CLOCK() - w0;
+                    if (kb == t.kb0 && u == static_cast<int>(blockIdx.x)) TB_PHASE(15);
                     mbar_arrive_expect_tx(full, kWeightRawBytes);
                     bulk_load(stage, codes, kBlockBytes, full);
                     if constexpr (kGroupScales) {

@@ -179,6 +179,7 @@ def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, ro
     args = call.args
     args.a, args.a_scale, args.d = a.data_ptr(), a_scale.data_ptr(), out.data_ptr()
     args.a_scale_stride_m, args.a_scale_stride_k = strides
+    args.status = _native.status_words(device.index).data_ptr()
     current = torch.cuda.current_device() == device.index
     stream = torch.cuda.current_stream(device).cuda_stream
     cfg_ref = call.cfg_ref
