@@ -11,8 +11,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBRARY = os.path.join(HERE, "libtensorbridge_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
-SOURCES = ["tb_api.cu", "tb_inst_w8_t1.cu", "tb_inst_w8_t2.cu", "tb_inst_w16_t4.cu"]
-HEADERS = ["tb_ptx.cuh", "tb_bridge.cuh", "tb_gemm.cuh", "tb_aux.cuh", "tb_launch.cuh", "tb_launch_impl.cuh", os.path.join("..", "..", "include", "tensorbridge_b200.h")]
+SOURCES = ["tb_api.cu", "tb_ep.cu", "tb_inst_w8_t1.cu", "tb_inst_w8_t2.cu", "tb_inst_w16_t4.cu"]
+HEADERS = ["tb_ptx.cuh", "tb_bridge.cuh", "tb_gemm.cuh", "tb_aux.cuh", "tb_launch.cuh", "tb_launch_impl.cuh", "tb_ep.cuh", os.path.join("..", "..", "include", "tensorbridge_b200.h")]
 
 
 def nvcc_path() -> str:

@@ -26,6 +26,21 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+}  // namespace
+
+namespace tb {
+// For the other translation units of the library: records the message tb_last_error() returns on this thread.
+int set_last_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+}  // namespace tb
+
+namespace {
+
 #define TB_CUDA(expr)                                                                                  \
     do {                                                                                               \
         cudaError_t err__ = (expr);                                                                    \

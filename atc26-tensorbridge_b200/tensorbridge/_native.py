@@ -90,6 +90,17 @@ SYMBOLS = {
     "tb_gemm_dense_static_scratch": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Config)]),
     "tb_gemm_grouped": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Routing),
                                        ctypes.POINTER(Config)]),
+    "tb_ep_plan": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                  ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+    "tb_ep_pack": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                  ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
+    "tb_ep_layout": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "tb_ep_place": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "tb_gather_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                      ctypes.c_void_p]),
 }
 
 

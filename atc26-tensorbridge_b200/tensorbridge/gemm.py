@@ -160,6 +160,32 @@ class _Call:
 
 
 _dense_calls: dict[tuple, _Call] = {}
+# Argument structs of dense calls whose every pointer is fixed (see `fp8_nvfp4_gemm`).
+_repeat_calls: dict[tuple, _Call] = {}
+
+
+def _relaunch(call: _Call, device: torch.device) -> None:
+    """Launch `call` again as it stands: only the stream, its split-K scratch and the status words are looked up."""
+    lib = _native.load()
+    args = call.args
+    args.status = _native.status_words(device.index).data_ptr()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    cfg_ref = call.cfg_ref
+    if call.need > 0:
+        workspace = _workspace(device, call.need, stream)
+        if workspace is None:
+            cfg_ref = call.unsplit_cfg_ref
+            args.workspace, args.workspace_bytes = None, 0
+        else:
+            args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
+    if torch.cuda.current_device() == device.index:
+        code = lib.tb_gemm_dense(stream, call.args_ref, cfg_ref)
+    else:
+        with torch.cuda.device(device):
+            code = lib.tb_gemm_dense(stream, call.args_ref, cfg_ref)
+    if code:
+        _native.check(code)
+
 
 
 def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, rows, n, k, bridge, group_scales,
@@ -217,6 +243,16 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
     `tensorbridge.experimental`) selects `[1,128]` activation scales `[M, K/128]` and the `[K/128, N, 8]` scale layout.
     """
     n, k = weight.shape
+    repeat_key = None
+    if out is not None:
+        # A call that repeats an earlier one pointer for pointer (a serving loop over static buffers) skips the checks
+        # it has passed before and relaunches with the argument structs of that call.
+        repeat_key = (weight.weight.data_ptr(), weight.scale.data_ptr(), n, k, weight.bridge, a.data_ptr(), a_scale.data_ptr(),
+                      out.data_ptr(), a.size(0), a.dtype, out.dtype, int(enable_pdl), config, group_scales)
+        again = _repeat_calls.get(repeat_key)
+        if again is not None and a.is_contiguous() and out.is_contiguous() and a_scale.size(0) == a.size(0):
+            _relaunch(again, a.device)
+            return out
     strides = _check_common(a, a_scale, k, group_scales)
     m = a.size(0)
     d = _output(out, m, n, a)
@@ -238,8 +274,13 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
         _require(weight.locks.dtype == torch.int32 and weight.locks.numel() >= 1024, "locks must be int32 [1024]")
         if len(_dense_calls) > 4096:
             _dense_calls.clear()
-    _dense_calls[key] = _launch(a, a_scale, strides, weight.weight, weight.scale, weight.global_scale, weight.locks, d, m, n,
-                                k, weight.bridge, group_scales, enable_pdl, config, None, call)
+    call = _dense_calls[key] = _launch(a, a_scale, strides, weight.weight, weight.scale, weight.global_scale, weight.locks, d,
+                                       m, n, k, weight.bridge, group_scales, enable_pdl, config, None, call)
+    if repeat_key is not None:
+        if len(_repeat_calls) > 4096:
+            _repeat_calls.clear()
+        _repeat_calls[repeat_key] = _Call(_native.GemmArgs.from_buffer_copy(call.args), _native.Config.from_buffer_copy(call.cfg),
+                                          None, call.need)
     return d
 
 

@@ -166,6 +166,10 @@ def dense_candidates(m: int, n: int, k: int, num_sms: int) -> list[GemmConfig]:
         tiles_m = [small] + ([small * 2] if small < 128 else [192])
     else:
         tiles_m = [192, 256] + ([128] if m <= 512 else [])
+        # narrow weights (column-parallel shards): wide tiles leave most SMs without a tile, so the narrower tiles and
+        # their K splits compete as well
+        if -(-m // 256) * n_tiles * 2 <= num_sms:
+            tiles_m += [bm for bm in (128, 64) if bm not in tiles_m and -(-m // bm) * n_tiles <= 128]
     for bm in tiles_m:
         base = _tile_defaults(bm, n, k, num_sms)
         tiles = -(-m // bm) * n_tiles

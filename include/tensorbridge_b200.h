@@ -238,6 +238,39 @@ typedef struct tb_routing {
  * Replaces launch_grouped_kernel, tensorbridge/csrc/launcher/launcher.cpp:471-478. */
 int tb_gemm_grouped(void* stream, const tb_gemm_args* args, const tb_routing* routing, const tb_config* config);
 
+/* ---- Expert-parallel token dispatch around the masked grouped GEMM (one process per GPU) ------------------------
+ * The reference has no counterpart for these five: it is handed expert-parallel shapes already dispatched by the
+ * serving framework (tensorbridge/vllm_moe.py:130-132).  They are the integer bookkeeping and the row movement on
+ * either side of the all-to-all exchange; the exchange itself (NCCL) stays with the caller.  World size W, E experts
+ * in all, E / W per rank; "placed" expert index = owner rank * (E / W) + local index, with owner = e / (E / W)
+ * (contiguous placement) or e % W (interleaved). */
+
+/* Routes of this rank -> send plan.  `topk_ids` int32 or int64 [routes] (route = token * top_k + slot; ids outside
+ * [0, E) are not sent); send_counts int32 [E] in placed order = [W][E / W]; send_pos int32 [routes] = row of the route
+ * in the send buffer, ordered by destination rank, then local expert, then route id (-1 = not sent).  E <= 1024. */
+int tb_ep_plan(void* stream, const void* topk_ids, int ids_int64, int64_t routes, int32_t num_experts, int32_t world,
+               int32_t interleaved, int32_t* send_counts, int32_t* send_pos);
+
+/* send[send_pos[r]] = { x[r / top_k] (width bytes of FP8), scale[r / top_k] (groups floats) } in rows of `row_bytes`
+ * (a multiple of 16, >= width + 4 * groups; width a multiple of 16): one exchange carries rows and scales. */
+int tb_ep_pack(void* stream, const void* x, const float* scale, const int32_t* send_pos, int64_t routes, int32_t top_k,
+               int64_t width, int64_t groups, int64_t row_bytes, void* send);
+
+/* recv_counts int32 [W][E / W] (rows received from every source rank for every local expert) -> seg_start and seg_dest
+ * int32 [W * E / W] (first row of every (source, expert) run in the receive buffer, and the masked-buffer row its
+ * first row goes to: expert * capacity + rows of earlier sources), counts int32 [E / W] = min(capacity, rows). */
+int tb_ep_layout(void* stream, const int32_t* recv_counts, int32_t world, int32_t experts_local, int32_t capacity,
+                 int32_t* seg_start, int32_t* seg_dest, int32_t* counts);
+
+/* Received packed rows -> masked activation buffer a [E / W * capacity, width] and a_scale [E / W * capacity, groups];
+ * recv_rows int32 [rows] = destination row of every received row, -1 for rows past their expert's capacity. */
+int tb_ep_place(void* stream, const void* recv, int64_t rows, int64_t row_bytes, int64_t width, int64_t groups,
+                const int32_t* seg_start, const int32_t* seg_dest, int32_t world, int32_t experts_local, int32_t capacity,
+                void* a, float* a_scale, int32_t* recv_rows);
+
+/* dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of `row_bytes` bytes (a multiple of 16). */
+int tb_gather_rows(void* stream, const void* src, const int32_t* index, int64_t rows, int64_t row_bytes, void* dst);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,24 +1,12 @@
-"""Seeded input builders shared by the GPU parity tests, the smoke test and the benchmark."""
+"""Oracle-side helpers shared by the GPU parity tests and the smoke test (the seeded input builders themselves live in
+`tensorbridge.synthetic`)."""
 from __future__ import annotations
 
 import numpy as np
 import torch
 
 
-def seeded_weight(n: int, k: int, seed: int, std: float = 0.02) -> torch.Tensor:
-    g = torch.Generator().manual_seed(seed)
-    return (torch.randn(n, k, generator=g) * std).bfloat16()
-
-
-def seeded_activations(m: int, k: int, seed: int, outliers: bool = True) -> torch.Tensor:
-    """BF16 N(0,1) activations with round(0.001 * K) seeded channels multiplied by 20."""
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randn(m, k, generator=g)
-    count = round(0.001 * k) if outliers else 0
-    if count:
-        idx = torch.randperm(k, generator=g)[:count]
-        x[:, idx] *= 20.0
-    return x.bfloat16()
+from tensorbridge.synthetic import seeded_activations, seeded_weight  # noqa: E402,F401  (re-exported for the tests)
 
 
 def oracle_weight(w: torch.Tensor, bridge: str) -> dict:
