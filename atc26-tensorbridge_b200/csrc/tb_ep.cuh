@@ -30,20 +30,21 @@ __device__ __forceinline__ int ep_load_id(const void* ids, bool ids_int64, long 
     return ids_int64 ? static_cast<int>(static_cast<const long long*>(ids)[i]) : static_cast<const int*>(ids)[i];
 }
 
-// Shared memory of the plan kernel, for E experts: int cursor[E], unsigned short tile_total[E],
+// Shared memory of the plan kernel, for E experts: int cursor[E], int first_row[E], unsigned short tile_total[E],
 // unsigned short prefix[kPlanWarps][E], unsigned char count[kPlanWarps][E].
 __host__ __device__ inline size_t ep_plan_smem(int experts) {
-    return static_cast<size_t>(experts) * (4 + 2 + kPlanWarps * 3) + 64 * 4;
+    return static_cast<size_t>(experts) * (4 + 4 + 2 + kPlanWarps * 3) + 64 * 4;
 }
 
 // One CTA.  Routes with an id outside [0, num_experts) are not sent: send_pos = -1.
 __global__ void __launch_bounds__(kPlanThreads, 1)
 ep_plan_kernel(const void* ids, int ids_int64, long long routes, int num_experts, int world, int interleaved,
-               int* __restrict__ send_counts, int* __restrict__ send_pos) {
+               int* __restrict__ send_counts, int* __restrict__ send_pos, int* __restrict__ route_rank) {
     extern __shared__ __align__(16) unsigned char plan_smem[];
     const int E = num_experts, e_local = E / world;
     int* cursor = reinterpret_cast<int*>(plan_smem);
-    int* warp_totals = cursor + E;  // 64 ints
+    int* first_row = cursor + E;      // first send row of every expert
+    int* warp_totals = first_row + E;  // 64 ints
     unsigned short* tile_total = reinterpret_cast<unsigned short*>(warp_totals + 64);
     unsigned short* prefix = tile_total + E;                                    // [kPlanWarps][E]
     unsigned char* count = reinterpret_cast<unsigned char*>(prefix + kPlanWarps * E);  // [kPlanWarps][E]
@@ -77,7 +78,7 @@ ep_plan_kernel(const void* ids, int ids_int64, long long routes, int num_experts
             warp_totals[32 + lane] = s - t;
         }
         __syncthreads();
-        if (tid < E) cursor[tid] = warp_totals[32 + warp] + incl - mine;
+        if (tid < E) cursor[tid] = first_row[tid] = warp_totals[32 + warp] + incl - mine;
     }
     __syncthreads();
 
@@ -105,7 +106,12 @@ ep_plan_kernel(const void* ids, int ids_int64, long long routes, int num_experts
             tile_total[e] = static_cast<unsigned short>(run);
         }
         __syncthreads();
-        if (r < routes) send_pos[r] = placed >= 0 ? cursor[placed] + prefix[warp * E + placed] + rank_in_warp : -1;
+        if (r < routes) {
+            const int pos = placed >= 0 ? cursor[placed] + prefix[warp * E + placed] + rank_in_warp : -1;
+            if (send_pos != nullptr) send_pos[r] = pos;
+            // rank of the route among this rank's routes to the same expert, in route order
+            if (route_rank != nullptr) route_rank[r] = placed >= 0 ? pos - first_row[placed] : -1;
+        }
         __syncthreads();
         for (int e = tid; e < E; e += kPlanThreads) cursor[e] += tile_total[e];
         // the zeroing pass of the next tile is separated from these reads by its own barrier
@@ -225,6 +231,141 @@ gather_rows16_kernel(const uint8_t* __restrict__ src, const int* __restrict__ in
             const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long long>(from) * row_bytes);
             for (int v = lane; v < row_bytes / 16; v += 32) out[v] = in[v];
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same dispatch over peer memory (NVLink loads and stores between the GPUs of one node) instead of an all-to-all:
+// every rank keeps its masked activation buffer, its output buffer, a [world][E] count matrix and a row of arrival flags
+// in memory its peers have mapped, and
+//   barrier  a rank-to-rank barrier on those flags, optionally carrying this rank's route counts to every peer first
+//   push     writes each route's FP8 row and scales straight into the masked buffer of the rank that owns its expert, at
+//            the row the layout rule gives it (expert block, then source rank, then route order); routes past an expert's
+//            capacity are never sent
+//   pull     reads each route's output row back from the owner's output buffer
+// so a step needs no host read, no staging copy and no collective library.  Plain loads and stores only.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kMaxPeers = 16;
+
+struct PeerPointers {
+    void* ptr[kMaxPeers];
+};
+
+// One CTA of 256 threads per launch.  Copies `count` ints from `payload` to row `rank` of every peer's [world][count]
+// matrix (when count > 0), then tells every peer "rank has arrived at barrier number e" and waits until every peer has
+// told it the same.  e is this rank's own count of barriers so far, kept in `local_epoch`: all ranks call the barrier the
+// same number of times.  The wait is bounded: when it runs out the kernel writes 100 + the peer it waited for to
+// status[0] and returns.
+__global__ void __launch_bounds__(256, 1)
+peer_barrier_kernel(PeerPointers flags, PeerPointers payload_dst, const int* __restrict__ payload, int count, int rank,
+                    int world, unsigned* local_epoch, long long wait_cycles, int* status) {
+    if (count > 0) {
+        for (int p = 0; p < world; ++p) {
+            int* dst = static_cast<int*>(payload_dst.ptr[p]) + static_cast<long long>(rank) * count;
+            for (int i = threadIdx.x; i < count; i += blockDim.x) dst[i] = payload[i];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ unsigned epoch;
+    if (threadIdx.x == 0) {
+        epoch = *local_epoch + 1u;
+        *local_epoch = epoch;
+    }
+    __syncthreads();
+    const unsigned e = epoch;
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        unsigned* theirs = static_cast<unsigned*>(flags.ptr[p]) + rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
+        const unsigned* mine = static_cast<const unsigned*>(flags.ptr[rank]) + p;
+        const long long start = clock64();
+        for (unsigned spin = 0;; ++spin) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (static_cast<int>(seen - e) >= 0) break;
+            if ((spin & 63u) == 63u && clock64() - start > wait_cycles) {
+                if (status != nullptr) atomicCAS(status, 0, 100 + p);
+                break;
+            }
+        }
+    }
+    __threadfence_system();
+}
+
+struct PushParams {
+    const void* ids;           // [routes] int32 or int64: global expert of every route
+    const uint8_t* x;          // [tokens, width] FP8
+    const float* scale;        // [tokens, groups]
+    const int* route_rank;     // [routes] from the plan kernel
+    const int* all_counts;     // [world][E] in placed order: routes of every source rank for every expert
+    int* dest_row;             // [routes] out: row in the owner's masked buffer, -1 = not sent
+    int* counts;               // [E / world] out: rows of this rank's own experts, clamped to the capacity
+    PeerPointers a, a_scale;   // every rank's masked buffers
+    long long routes;
+    int ids_int64, top_k, num_experts, world, rank, interleaved, capacity, width, groups;
+};
+
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const PushParams p) {
+    const int lane = threadIdx.x & 31;
+    const int e_local = p.num_experts / p.world;
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
+            int total = 0;
+            for (int s = 0; s < p.world; ++s) total += p.all_counts[s * p.num_experts + p.rank * e_local + e];
+            p.counts[e] = min(total, p.capacity);
+        }
+    }
+    const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    for (long long r = warp0; r < p.routes; r += warps) {
+        const int e = ep_load_id(p.ids, p.ids_int64 != 0, r);
+        int row = -1, owner = 0;
+        if (e >= 0 && e < p.num_experts) {
+            const int placed = ep_placed(e, e_local, p.world, p.interleaved != 0);
+            owner = placed / e_local;
+            int slot = p.route_rank[r];
+            for (int s = 0; s < p.rank; ++s) slot += p.all_counts[s * p.num_experts + placed];
+            if (slot < p.capacity) row = (placed - owner * e_local) * p.capacity + slot;
+        }
+        if (lane == 0) p.dest_row[r] = row;
+        if (row < 0) continue;
+        const long long token = r / p.top_k;
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + token * p.width);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.a.ptr[owner]) + static_cast<long long>(row) * p.width);
+        for (int i = lane; i < p.width / 16; i += 32) dst[i] = src[i];
+        float* sdst = static_cast<float*>(p.a_scale.ptr[owner]) + static_cast<long long>(row) * p.groups;
+        for (int g = lane; g < p.groups; g += 32) sdst[g] = p.scale[token * p.groups + g];
+    }
+}
+
+struct PullParams {
+    const void* ids;
+    const int* dest_row;   // [routes] from the push kernel
+    PeerPointers y;        // every rank's output buffer [E / world * capacity, row_bytes]
+    uint8_t* out;          // [routes, row_bytes]
+    long long routes;
+    int ids_int64, num_experts, world, interleaved, row_bytes;
+};
+
+__global__ void __launch_bounds__(256)
+ep_pull_kernel(const PullParams p) {
+    const int lane = threadIdx.x & 31;
+    const int e_local = p.num_experts / p.world;
+    const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    for (long long r = warp0; r < p.routes; r += warps) {
+        const int row = p.dest_row[r];
+        uint4* out = reinterpret_cast<uint4*>(p.out + r * p.row_bytes);
+        if (row < 0) {
+            for (int v = lane; v < p.row_bytes / 16; v += 32) out[v] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const int e = ep_load_id(p.ids, p.ids_int64 != 0, r);
+        const int owner = ep_placed(e, e_local, p.world, p.interleaved != 0) / e_local;
+        const uint4* in = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.y.ptr[owner]) + static_cast<long long>(row) * p.row_bytes);
+        for (int v = lane; v < p.row_bytes / 16; v += 32) out[v] = in[v];
     }
 }
 

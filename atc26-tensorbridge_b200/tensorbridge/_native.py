@@ -67,6 +67,19 @@ class QuantMoeArgs(ctypes.Structure):
     ]
 
 
+class PushArgs(ctypes.Structure):
+    """`tb_ep_push_args`."""
+
+    _fields_ = [
+        ("topk_ids", ctypes.c_void_p), ("ids_int64", ctypes.c_int32), ("top_k", ctypes.c_int32), ("routes", ctypes.c_int64),
+        ("x", ctypes.c_void_p), ("scale", ctypes.c_void_p), ("width", ctypes.c_int64), ("groups", ctypes.c_int64),
+        ("route_rank", ctypes.c_void_p), ("all_counts", ctypes.c_void_p), ("num_experts", ctypes.c_int32),
+        ("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("interleaved", ctypes.c_int32), ("capacity", ctypes.c_int32),
+        ("reserved", ctypes.c_int32), ("peer_a", ctypes.POINTER(ctypes.c_void_p)), ("peer_a_scale", ctypes.POINTER(ctypes.c_void_p)),
+        ("dest_row", ctypes.c_void_p), ("counts", ctypes.c_void_p),
+    ]
+
+
 # Every symbol include/tensorbridge_b200.h declares: (restype, argtypes).
 SYMBOLS = {
     "tb_last_error": (ctypes.c_char_p, []),
@@ -91,7 +104,7 @@ SYMBOLS = {
     "tb_gemm_grouped": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Routing),
                                        ctypes.POINTER(Config)]),
     "tb_ep_plan": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
-                                  ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]),
+                                  ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tb_ep_pack": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                   ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]),
     "tb_ep_layout": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
@@ -101,6 +114,17 @@ SYMBOLS = {
                                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tb_gather_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                       ctypes.c_void_p]),
+    "tb_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]),
+    "tb_peer_free": (ctypes.c_int, [ctypes.c_void_p]),
+    "tb_ipc_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),
+    "tb_ipc_open": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "tb_ipc_close": (ctypes.c_int, [ctypes.c_void_p]),
+    "tb_peer_barrier": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                       ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                       ctypes.c_int32, ctypes.c_void_p]),
+    "tb_ep_push": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(PushArgs)]),
+    "tb_ep_pull": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32,
+                                  ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_void_p]),
 }
 
 

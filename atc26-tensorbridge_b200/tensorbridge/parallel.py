@@ -15,7 +15,9 @@ CPU tensors the same plan is worked out with torch ops, which is also what the G
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
+import os
 
 import torch
 import torch.distributed as dist
@@ -131,7 +133,7 @@ def _plan_native(x_q, x_scale, topk_ids, num_experts, world, placement, row_byte
     with torch.cuda.device(device):
         stream = _native.stream_ptr(device)
         _native.check(lib.tb_ep_plan(stream, ids.data_ptr(), int(ids.dtype == torch.int64), routes, num_experts, world,
-                                     int(placement == "interleaved"), send_counts.data_ptr(), send_pos.data_ptr()))
+                                     int(placement == "interleaved"), send_counts.data_ptr(), send_pos.data_ptr(), None))
         _native.check(lib.tb_ep_pack(stream, x_q.data_ptr(), scale.data_ptr(), send_pos.data_ptr(), routes, top_k, width, groups,
                                      row_bytes, send.data_ptr()))
     return send_counts, send_pos, send
@@ -245,3 +247,157 @@ def combine_masked(local_out: torch.Tensor, plan: MaskedDispatch, num_routes: in
     if plan.send_pos.numel() != num_routes:
         raise ValueError(f"the plan covers {plan.send_pos.numel()} routes, not {num_routes}")
     return gather_rows(returned, plan.send_pos)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The same step over peer memory: each rank writes its routes straight into the owner's masked buffer and reads the
+# results back from the owner's output buffer (NVLink loads and stores issued by the library's kernels), with rank-to-rank
+# barriers on flags in that memory.  No collective library call, no host read, no staging copy in a step.
+# ---------------------------------------------------------------------------------------------------------------------
+class _DeviceView:
+    """`__cuda_array_interface__` over raw device memory, so that torch can alias it as a tensor."""
+
+    def __init__(self, pointer: int, shape: tuple, typestr: str) -> None:
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (pointer, False), "version": 2}
+
+
+def _alias(pointer: int, shape: tuple, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    typestr, view = {torch.uint8: ("|u1", None), torch.float32: ("<f4", None), torch.int32: ("<i4", None),
+                     torch.bfloat16: ("<u2", torch.bfloat16), torch.float8_e4m3fn: ("|u1", torch.float8_e4m3fn)}[dtype]
+    t = torch.as_tensor(_DeviceView(pointer, shape, typestr), device=device)
+    return t if view is None else t.view(view)
+
+
+@dataclasses.dataclass
+class PeerDispatch:
+    """What `PeerMaskedExchange.dispatch` returns: the masked GEMM inputs (views of this rank's peer-mapped buffers)."""
+
+    a: torch.Tensor  # FP8 [E_local * capacity, K]
+    a_scale: torch.Tensor  # FP32 [E_local * capacity, groups]
+    counts: torch.Tensor  # int32 [E_local], clamped to capacity
+    out: torch.Tensor  # BF16 [E_local * capacity, N]: where the masked GEMM must write (`out=`)
+    dest_row: torch.Tensor  # int32 [T * top_k]: row of every route in its owner's buffers (-1 = dropped)
+    topk_ids: torch.Tensor
+
+
+class PeerMaskedExchange:
+    """Expert-parallel masked dispatch and combine over peer memory for a fixed (experts, capacity, K, groups, N).
+
+    Construction is collective (every rank of `group`, same arguments): each rank allocates one slab (masked
+    activations, their scales, the GEMM output, a `[world, E]` count matrix, arrival flags), exports it and maps its
+    peers' slabs (CUDA IPC; all ranks on one node, one GPU each).  A step is
+
+        plan = exchange.dispatch(x_q, x_scale, topk_ids)            # plan, barrier (+ counts), push, barrier
+        tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, experts, tb.MaskedRouting(plan.counts), m, out=plan.out)
+        y = exchange.combine(plan)                                   # barrier, pull
+
+    and launches nothing but this library's kernels: no host read, so it can follow a quantiser and precede the next
+    layer without a synchronisation.  The masked buffers are reused by the next `dispatch`: consume `y` (a fresh
+    tensor) as you like, but read `plan.a` / `plan.out` only before the next step.  `close()` unmaps and frees."""
+
+    def __init__(self, num_experts: int, capacity: int, k: int, groups: int, n: int, group=None,
+                 placement: str = "interleaved", wait_us: int = 0) -> None:
+        from tensorbridge import _native  # noqa: PLC0415
+        self._native, self._lib = _native, _native.load()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if num_experts % self.world:
+            raise ValueError(f"{num_experts} experts do not split over {self.world} ranks")
+        if placement not in ("contiguous", "interleaved"):
+            raise ValueError(f"unknown placement {placement!r}")
+        if k % 16 or (2 * n) % 16:
+            raise ValueError("K must be a multiple of 16 and N of 8")
+        self.num_experts, self.capacity, self.k, self.groups, self.n = num_experts, capacity, k, groups, n
+        self.e_local = num_experts // self.world
+        self.placement, self.wait_us = placement, wait_us
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        rows = self.e_local * capacity
+        sizes = [rows * k, rows * groups * 4, rows * n * 2, self.world * num_experts * 4, 256]
+        self._offsets, total = [], 0
+        for size in sizes:
+            self._offsets.append(total)
+            total += (size + 255) // 256 * 256
+        base = ctypes.c_void_p()
+        _native.check(self._lib.tb_peer_alloc(total, ctypes.byref(base)))
+        self._base = base.value
+        handle = ctypes.create_string_buffer(64)
+        _native.check(self._lib.tb_ipc_export(self._base, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (os.getpid(), handle.raw), group=group)
+        self._peer_bases, self._opened = [], []
+        for r, (pid, raw) in enumerate(handles):
+            if r == self.rank or pid == os.getpid():
+                self._peer_bases.append(self._base)
+                continue
+            mapped = ctypes.c_void_p()
+            _native.check(self._lib.tb_ipc_open(raw, ctypes.byref(mapped)))
+            self._peer_bases.append(mapped.value)
+            self._opened.append(mapped.value)
+
+        def pointers(index: int):
+            return (ctypes.c_void_p * self.world)(*[b + self._offsets[index] for b in self._peer_bases])
+
+        self._peer_a, self._peer_scale, self._peer_y = pointers(0), pointers(1), pointers(2)
+        self._peer_counts, self._peer_flags = pointers(3), pointers(4)
+        self.a = _alias(self._base + self._offsets[0], (rows, k), torch.float8_e4m3fn, self.device)
+        self.a_scale = _alias(self._base + self._offsets[1], (rows, groups), torch.float32, self.device)
+        self.out = _alias(self._base + self._offsets[2], (rows, n), torch.bfloat16, self.device)
+        self.all_counts = _alias(self._base + self._offsets[3], (self.world, num_experts), torch.int32, self.device)
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._send_counts = torch.empty(num_experts, dtype=torch.int32, device=self.device)
+        self.counts = torch.empty(self.e_local, dtype=torch.int32, device=self.device)
+        dist.barrier(group=group)  # every rank has mapped every slab before anybody writes into one
+
+    def _barrier(self, stream: int, payload: torch.Tensor | None = None) -> None:
+        native = self._native
+        native.check(self._lib.tb_peer_barrier(
+            stream, self._peer_flags, self._peer_counts, None if payload is None else payload.data_ptr(),
+            0 if payload is None else payload.numel(), self.rank, self.world, self._epoch.data_ptr(), self.wait_us,
+            native.status_words(self.device.index).data_ptr()))
+
+    def dispatch(self, x_q: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor) -> PeerDispatch:
+        native = self._native
+        t, top_k = topk_ids.shape
+        if x_q.size(1) != self.k or x_scale.reshape(t, -1).size(1) != self.groups or not x_q.is_contiguous():
+            raise ValueError("activations do not match the exchange's K / scale groups")
+        ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) and topk_ids.is_contiguous() else topk_ids.to(torch.int64).contiguous()
+        scale = x_scale.reshape(t, -1).contiguous()
+        routes = t * top_k
+        route_rank = torch.empty(routes, dtype=torch.int32, device=self.device)
+        dest_row = torch.empty(routes, dtype=torch.int32, device=self.device)
+        interleaved = int(self.placement == "interleaved")
+        with torch.cuda.device(self.device):
+            stream = native.stream_ptr(self.device)
+            native.check(self._lib.tb_ep_plan(stream, ids.data_ptr(), int(ids.dtype == torch.int64), routes, self.num_experts,
+                                              self.world, interleaved, self._send_counts.data_ptr(), None, route_rank.data_ptr()))
+            self._barrier(stream, self._send_counts)  # every rank now holds every rank's counts
+            args = native.PushArgs(ids.data_ptr(), int(ids.dtype == torch.int64), top_k, routes, x_q.data_ptr(), scale.data_ptr(),
+                                   self.k, self.groups, route_rank.data_ptr(), self.all_counts.data_ptr(), self.num_experts,
+                                   self.world, self.rank, interleaved, self.capacity, 0, self._peer_a, self._peer_scale,
+                                   dest_row.data_ptr(), self.counts.data_ptr())
+            native.check(self._lib.tb_ep_push(stream, ctypes.byref(args)))
+            self._barrier(stream)  # every rank's rows have landed
+        return PeerDispatch(self.a, self.a_scale, self.counts, self.out, dest_row, ids)
+
+    def combine(self, plan: PeerDispatch) -> torch.Tensor:
+        """`[T * top_k, N]` in route order: every route's row of the owner's GEMM output, zeros for dropped routes."""
+        native = self._native
+        routes = plan.dest_row.numel()
+        out = torch.empty((routes, self.n), dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            stream = native.stream_ptr(self.device)
+            self._barrier(stream)  # every rank's GEMM has written its output buffer
+            native.check(self._lib.tb_ep_pull(stream, plan.topk_ids.data_ptr(), int(plan.topk_ids.dtype == torch.int64),
+                                              plan.dest_row.data_ptr(), routes, self.num_experts, self.world,
+                                              int(self.placement == "interleaved"), self._peer_y, self.n * 2, out.data_ptr()))
+        return out
+
+    def close(self) -> None:
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody still reads or writes a peer's slab
+        for pointer in self._opened:
+            self._native.check(self._lib.tb_ipc_close(pointer))
+        self._native.check(self._lib.tb_peer_free(self._base))
+        self._base, self._opened = None, []

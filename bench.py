@@ -506,33 +506,59 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
             x = synthetic.seeded_activations(local_tokens, k, seed=2000 + tokens + rank).to(dev)
             gemm_start, gemm_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             gemm_ms = []
+            routes = local_tokens * top_k
 
-            def ep_step(timed: bool = False):
+            def collective_step(timed: bool = False):
                 q, s = fp8.quantize(x)
                 plan = parallel.dispatch_masked(q, s, ids, experts, capacity, placement="interleaved")
                 gemm_start.record()
-                y = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), local_tokens * top_k)
+                y = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), routes)
                 gemm_stop.record()
-                result = parallel.combine_masked(y, plan, local_tokens * top_k)
+                result = parallel.combine_masked(y, plan, routes)
                 if timed:
                     gemm_stop.synchronize()
                     gemm_ms.append(gemm_start.elapsed_time(gemm_stop))
                 return result, plan
 
-            result, plan = ep_step()
+            exchange, why_not = None, None
+            try:
+                exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement="interleaved")
+            except Exception as exc:  # noqa: BLE001  peer mapping unavailable on this box: the collective path is timed alone
+                why_not = f"{type(exc).__name__}: {exc}"
+            usable = torch.tensor([exchange is not None], device=dev, dtype=torch.int32)
+            dist.all_reduce(usable, op=dist.ReduceOp.MIN)
+            if not bool(usable.item()) and exchange is not None:
+                exchange.close()
+                exchange = None
+
+            def peer_step(timed: bool = False, events: bool = True):
+                q, s = fp8.quantize(x)
+                plan = exchange.dispatch(q, s, ids)
+                if events:
+                    gemm_start.record()
+                tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), routes, out=plan.out)
+                if events:
+                    gemm_stop.record()
+                result = exchange.combine(plan)
+                if timed:
+                    gemm_stop.synchronize()
+                    gemm_ms.append(gemm_start.elapsed_time(gemm_stop))
+                return result, plan
+
+            result, plan = collective_step()
             kept = int((plan.recv_rows >= 0).sum())
             # Checks of the first step.  Dispatch and combine with the identity as expert: the first 64 FP8 bytes of every
             # row, sent to its expert's rank and back, must return to the route they left from (or as zeros, when the
             # route fell past its expert's capacity); over all ranks as many routes return as were kept.
             q0, _ = fp8.quantize(x)
-            echo = parallel.combine_masked(plan.a.view(torch.uint8)[:, :64].to(torch.bfloat16).contiguous(), plan, local_tokens * top_k)
+            echo = parallel.combine_masked(plan.a.view(torch.uint8)[:, :64].to(torch.bfloat16).contiguous(), plan, routes)
             want = q0.view(torch.uint8)[:, :64].to(torch.bfloat16).repeat_interleave(top_k, 0)
             same, zero = (echo == want).all(1), (echo == 0).all(1)
             returned = sum_over_ranks(int((same & ~zero).sum()))
             if not bool((same | zero).all()) or returned > sum_over_ranks(kept) or returned < 0.98 * sum_over_ranks(kept):
                 raise SystemExit(f"expert-parallel round trip failed at T = {local_tokens * world} on rank {rank}")
             # and the grouped GEMM on what was received: every expert's rows against an FP32 product of the same operands
-            y0 = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), local_tokens * top_k)
+            y0 = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), routes)
             bridged = nvfp4.bridged_fp8(ex)
             for e in range(0, e_local, max(e_local // 8, 1)):
                 c = int(plan.counts[e])
@@ -543,28 +569,74 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
                     if err > TOL:
                         raise SystemExit(f"expert-parallel GEMM parity failed: T = {local_tokens * world}, rank {rank}, expert {e}: {err:.3e}")
             del bridged, y0, echo, want
-            for _ in range(3):
-                ep_step()
-            dist.barrier(); torch.cuda.synchronize()
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 10
-            start.record()
-            for _ in range(reps):
-                ep_step(True)
-            stop.record(); stop.synchronize()
-            step_ms = max_over_ranks(start.elapsed_time(stop) / reps)
-            g_ms = max_over_ranks(sum(gemm_ms) / len(gemm_ms))
+            # the exchange over peer memory must return what the collective path returns, bit for bit
+            if exchange is not None:
+                peer_result, _ = peer_step()
+                if not torch.equal(peer_result, result):
+                    raise SystemExit(f"peer-memory exchange disagrees with the collective path at T = {local_tokens * world} on rank {rank}")
+                tb.check_status()
+
+            def time_steps(step):
+                gemm_ms.clear()
+                for _ in range(3):
+                    step()
+                dist.barrier(); torch.cuda.synchronize()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 10
+                start.record()
+                for _ in range(reps):
+                    step(True)
+                stop.record(); stop.synchronize()
+                return max_over_ranks(start.elapsed_time(stop) / reps), max_over_ranks(sum(gemm_ms) / len(gemm_ms))
+
+            nccl_ms, nccl_gemm_ms = time_steps(collective_step)
+            step_ms, g_ms = time_steps(peer_step) if exchange is not None else (nccl_ms, nccl_gemm_ms)
+            graph_ms = None
+            if exchange is not None:
+                # the whole step reads nothing back to the host, so it replays from one CUDA graph per rank
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    peer_step(events=False)
+                    side.synchronize()
+                    step_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(step_graph, stream=side):
+                        graph_result, _ = peer_step(events=False)
+                    for _ in range(3):
+                        step_graph.replay()
+                    side.synchronize()
+                    if not torch.equal(graph_result, result):
+                        raise SystemExit(f"replayed expert-parallel step disagrees at T = {local_tokens * world} on rank {rank}")
+                    dist.barrier(); torch.cuda.synchronize()
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(side)
+                    for _ in range(20):
+                        step_graph.replay()
+                    stop.record(side); stop.synchronize()
+                graph_ms = max_over_ranks(start.elapsed_time(stop) / 20)
+                torch.cuda.current_stream(dev).wait_stream(side)
+                tb.check_status()
+                del step_graph, graph_result
+            best_ms = min(step_ms, graph_ms) if graph_ms is not None else step_ms
             routed = sum_over_ranks(kept)
-            rows_out.append({"tokens": local_tokens * world, "capacity": capacity, "step_ms": round(step_ms, 4), "gemm_ms": round(g_ms, 4),
-                             "dispatch_combine_ms": round(step_ms - g_ms, 4), "tokens_per_s": round(local_tokens * world / step_ms * 1e3, 1),
-                             "routes_kept": int(routed), "routes": local_tokens * world * top_k,
+            rows_out.append({"tokens": local_tokens * world, "capacity": capacity,
+                             "exchange": "peer memory (NVLink loads/stores by the library's kernels)" if exchange is not None
+                                         else f"NCCL all-to-all (peer mapping unavailable: {why_not})",
+                             "step_ms": round(step_ms, 4), "gemm_ms": round(g_ms, 4),
+                             "dispatch_combine_ms": round(step_ms - g_ms, 4),
+                             "step_ms_graph": None if graph_ms is None else round(graph_ms, 4),
+                             "tokens_per_s": round(local_tokens * world / best_ms * 1e3, 1), "step_ms_nccl": round(nccl_ms, 4), "routes_kept": int(routed), "routes": local_tokens * world * top_k,
                              "gemm_tflops": round(2.0 * routed * n * k / g_ms / 1e9, 1)})
+            if exchange is not None:
+                exchange.close()
             del result, plan
         tb.check_status()
         out["moe_masked_expert_parallel"] = {
             "config": "benchmark config 3: E=256 (E/n_gpus per GPU, interleaved placement), N=4096, K=7168, top_k=8, Zipf(1.1) routing; "
-                      "fp8.quantize -> all-to-all dispatch (counts, then packed FP8 rows + scales) -> masked grouped GEMM -> "
-                      "gather + all-to-all combine; scaling: strong in tokens, weights sharded",
+                      "step = fp8.quantize -> dispatch -> masked grouped GEMM -> combine; over peer memory (plan, barrier carrying the "
+                      "counts, push, barrier, GEMM, barrier, pull: no host read) and, as step_ms_nccl, over NCCL (counts all-to-all, host "
+                      "read of the split sizes, packed-row all-to-all, place, GEMM, gather, all-to-all, gather); strong scaling in tokens, "
+                      "weights sharded",
             "experts_per_gpu": e_local, "results": rows_out}
         del ex
         torch.cuda.empty_cache()

@@ -1,7 +1,7 @@
 /* C ABI of libtensorbridge_b200.so: FP8-activation x NVFP4-weight GEMMs for NVIDIA B200 (sm_100a).
  *
  * Every entry point takes plain device pointers, sizes and a `cudaStream_t` passed as `void*`; none allocates,
- * frees, synchronises or throws.  The return value is 0 on success or one of the TB_ERR_* codes below, with a
+ * frees, synchronises or throws (the four set-up helpers for peer memory at the end of this file excepted).  The return value is 0 on success or one of the TB_ERR_* codes below, with a
  * human-readable message available from tb_last_error() (thread-local).  The caller owns every buffer, the
  * output included, so a launch is allocation-free and can be captured in a CUDA graph.
  *
@@ -247,9 +247,11 @@ int tb_gemm_grouped(void* stream, const tb_gemm_args* args, const tb_routing* ro
 
 /* Routes of this rank -> send plan.  `topk_ids` int32 or int64 [routes] (route = token * top_k + slot; ids outside
  * [0, E) are not sent); send_counts int32 [E] in placed order = [W][E / W]; send_pos int32 [routes] = row of the route
- * in the send buffer, ordered by destination rank, then local expert, then route id (-1 = not sent).  E <= 1024. */
+ * in the send buffer, ordered by destination rank, then local expert, then route id (-1 = not sent); route_rank int32
+ * [routes] = rank of the route among this rank's routes to the same expert, in route order (either output may be
+ * NULL).  E <= 1024. */
 int tb_ep_plan(void* stream, const void* topk_ids, int ids_int64, int64_t routes, int32_t num_experts, int32_t world,
-               int32_t interleaved, int32_t* send_counts, int32_t* send_pos);
+               int32_t interleaved, int32_t* send_counts, int32_t* send_pos, int32_t* route_rank);
 
 /* send[send_pos[r]] = { x[r / top_k] (width bytes of FP8), scale[r / top_k] (groups floats) } in rows of `row_bytes`
  * (a multiple of 16, >= width + 4 * groups; width a multiple of 16): one exchange carries rows and scales. */
@@ -270,6 +272,65 @@ int tb_ep_place(void* stream, const void* recv, int64_t rows, int64_t row_bytes,
 
 /* dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of `row_bytes` bytes (a multiple of 16). */
 int tb_gather_rows(void* stream, const void* src, const int32_t* index, int64_t rows, int64_t row_bytes, void* dst);
+
+/* ---- The same dispatch over peer memory: NVLink loads and stores between the GPUs of one node, no collective library,
+ * no host read, no staging copy.  No counterpart in the reference (its overlap.py streams tokens into a masked buffer
+ * from one producer on the same GPU, tensorbridge/overlap.py:110-180).  Every rank owns, in memory its peers have
+ * mapped: the masked activation buffer a [E/W * capacity, width] and a_scale [E/W * capacity, groups], the output
+ * buffer y [E/W * capacity, n], a count matrix int32 [W][E] and W arrival flags (uint32, zero at start).  One step:
+ *   tb_ep_plan (route_rank, send_counts) -> tb_peer_barrier carrying send_counts into row `rank` of every peer's count
+ *   matrix -> tb_ep_push -> tb_peer_barrier -> tb_gemm_grouped (masked) into y -> tb_peer_barrier -> tb_ep_pull.
+ * Only plain loads and stores cross NVLink (no TMA on peer memory, no multicast). */
+
+/* Set-up helpers for that memory.  These four are the only entry points of the library that allocate, free or map
+ * memory; none of them belongs on a hot path.  tb_peer_alloc returns zeroed device memory from cudaMalloc (the kind
+ * cudaIpcGetMemHandle accepts); a handle is 64 bytes; tb_ipc_open maps a peer's allocation into this process with the
+ * current device as the accessing device (peer access is enabled on first use). */
+int tb_peer_alloc(int64_t bytes, void** ptr);
+int tb_peer_free(void* ptr);
+int tb_ipc_export(const void* ptr, uint8_t* handle);
+int tb_ipc_open(const uint8_t* handle, void** ptr);
+int tb_ipc_close(void* ptr);
+
+/* Barrier between the ranks' streams on the flags above (flags[p] = rank p's flag array, as mapped here), optionally
+ * copying `count` ints from `payload` to row `rank` of every peer's [W][count] matrix payload_dst[p] first.  Every rank
+ * calls it the same number of times; `local_epoch` (device uint32, zero at start, this rank's own) counts them.  A wait
+ * that lasts longer than `wait_us` microseconds (0 = about a second) ends the kernel with 100 + the missing peer in
+ * status[0].  Kernels of different ranks wait for one another here: every rank must run on a GPU of its own. */
+int tb_peer_barrier(void* stream, void* const* flags, void* const* payload_dst, const int32_t* payload, int32_t count,
+                    int32_t rank, int32_t world, uint32_t* local_epoch, int32_t wait_us, int32_t* status);
+
+/* Writes every route's FP8 row and scales into the masked buffer of the rank that owns its expert: row = local expert
+ * * capacity + routes of lower ranks for that expert + route_rank; routes past the capacity are not sent.  dest_row
+ * int32 [routes] receives the row (-1 = not sent); counts int32 [E/W] the rows of this rank's own experts, clamped. */
+typedef struct tb_ep_push_args {
+    const void* topk_ids;      /* int32 or int64 [routes] */
+    int32_t ids_int64;
+    int32_t top_k;
+    int64_t routes;
+    const void* x;             /* FP8 [routes / top_k, width] */
+    const float* scale;        /* FP32 [routes / top_k, groups] */
+    int64_t width;
+    int64_t groups;
+    const int32_t* route_rank; /* from tb_ep_plan */
+    const int32_t* all_counts; /* this rank's count matrix [W][E], filled by the barrier before */
+    int32_t num_experts;
+    int32_t world;
+    int32_t rank;
+    int32_t interleaved;
+    int32_t capacity;
+    int32_t reserved;
+    void* const* peer_a;       /* host array of W device pointers: every rank's masked activation buffer */
+    void* const* peer_a_scale; /* ... and scale buffer */
+    int32_t* dest_row;
+    int32_t* counts;
+} tb_ep_push_args;
+
+int tb_ep_push(void* stream, const tb_ep_push_args* args);
+
+/* out[r] = dest_row[r] >= 0 ? (owner of route r).y[dest_row[r]] : zeros; rows of `row_bytes` bytes (multiple of 16). */
+int tb_ep_pull(void* stream, const void* topk_ids, int ids_int64, const int32_t* dest_row, int64_t routes, int32_t num_experts,
+               int32_t world, int32_t interleaved, void* const* peer_y, int64_t row_bytes, void* out);
 
 #ifdef __cplusplus
 }

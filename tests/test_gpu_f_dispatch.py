@@ -81,50 +81,99 @@ def test_gather_rows_kernel():
         parallel.gather_rows(src[:, :5].contiguous(), index)
 
 
-def test_dispatch_then_masked_gemm_then_combine_on_one_rank():
-    """The whole expert-parallel step with a world of one process (NCCL all-to-all with itself): every route comes back
-    with the output row the masked grouped GEMM computed for it, routes over an expert's capacity come back as zeros."""
+@pytest.fixture(scope="module")
+def one_rank_group():
     import os
     import torch.distributed as dist
-    import tb_oracle as orc
-    import tensorbridge as tb
-    from helpers import oracle_weight, seeded_activations, seeded_weight
-    from tensorbridge import parallel
-    from tensorbridge.quant import fp8, nvfp4
     created = not dist.is_initialized()
     if created:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", str(29700 + os.getpid() % 200))
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    yield dist
+    if created:
+        dist.destroy_process_group()
+
+
+def _moe_case(experts, n, k, tokens, top_k, probabilities, seed):
+    import tb_oracle as orc
+    from helpers import oracle_weight, seeded_activations, seeded_weight
+    from tensorbridge.quant import fp8, nvfp4
+    views = [oracle_weight(seeded_weight(n, k, seed=seed + e), "exact") for e in range(experts)]
+    ex = nvfp4.prepare_experts(torch.stack([torch.from_numpy(v["packed"]) for v in views]).cuda(),
+                               torch.stack([torch.from_numpy(v["scale"]) for v in views]).cuda().view(torch.float8_e4m3fn),
+                               torch.cat([torch.from_numpy(v["global_scale"]) for v in views]).cuda(), bridge="exact")
+    x = seeded_activations(tokens, k, seed=seed + 99)
+    q, s = fp8.quantize(x.cuda())
+    rng = np.random.default_rng(5)
+    ids = torch.from_numpy(np.stack([rng.choice(experts, size=top_k, replace=False, p=probabilities) for _ in range(tokens)])).cuda()
+    wq, ws = orc.quantize_fp8_per_token(x)
+    return views, ex, q, s, ids, wq, ws
+
+
+def _check_routes(back, ids, views, wq, ws, capacity, n, k, top_k):
+    import tb_oracle as orc
+    flat = ids.reshape(-1).cpu().numpy()
+    seen = {e: 0 for e in range(len(views))}
+    dropped = 0
+    for r, e in enumerate(flat):
+        seen[e] += 1
+        row = back[r].float().cpu()
+        if seen[e] > capacity:
+            assert bool((row == 0).all())
+            dropped += 1
+            continue
+        t = r // top_k
+        want = orc.gemm_dense(wq[t:t + 1], ws[t:t + 1], views[e]["fp8"], float(views[e]["global_scale6"][0]), n, k)[0].float()
+        assert float((row - want).abs().max()) <= float(want.abs().max()) * 2 ** -6
+    return dropped
+
+
+def test_dispatch_then_masked_gemm_then_combine_on_one_rank(one_rank_group):
+    """The whole expert-parallel step with a world of one process (NCCL all-to-all with itself): every route comes back
+    with the output row the masked grouped GEMM computed for it, routes over an expert's capacity come back as zeros."""
+    import tensorbridge as tb
+    from tensorbridge import parallel
+    experts, n, k, tokens, top_k, capacity = 4, 128, 256, 24, 2, 8
+    views, ex, q, s, ids, wq, ws = _moe_case(experts, n, k, tokens, top_k, [0.55, 0.25, 0.1, 0.1], seed=600)
+    plan = parallel.dispatch_masked(q, s, ids, experts, capacity)
+    y = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), tokens * top_k)
+    back = parallel.combine_masked(y, plan, tokens * top_k)
+    tb.check_status()
+    assert _check_routes(back, ids, views, wq, ws, capacity, n, k, top_k) > 0  # the skewed routing overfills the first expert
+
+
+@pytest.mark.parametrize("placement", ["contiguous", "interleaved"])
+def test_peer_memory_exchange_matches_the_collective_path(one_rank_group, placement):
+    """The same step over peer memory (`PeerMaskedExchange`: plan, barrier carrying the counts, push, barrier, GEMM,
+    barrier, pull): the masked buffers hold the same rows in the same places as the all-to-all path builds, and the
+    combined output is the same, over two steps with different routing (the buffers and the barrier count are reused)."""
+    import tensorbridge as tb
+    from tensorbridge import parallel
+    experts, n, k, tokens, top_k, capacity = 4, 128, 256, 24, 2, 8
+    views, ex, q, s, ids, wq, ws = _moe_case(experts, n, k, tokens, top_k, [0.55, 0.25, 0.1, 0.1], seed=700)
+    exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement=placement, wait_us=2_000_000)
     try:
-        experts, n, k, tokens, top_k, capacity = 4, 128, 256, 24, 2, 8
-        views = [oracle_weight(seeded_weight(n, k, seed=600 + e), "exact") for e in range(experts)]
-        ex = nvfp4.prepare_experts(torch.stack([torch.from_numpy(v["packed"]) for v in views]).cuda(),
-                                   torch.stack([torch.from_numpy(v["scale"]) for v in views]).cuda().view(torch.float8_e4m3fn),
-                                   torch.cat([torch.from_numpy(v["global_scale"]) for v in views]).cuda(), bridge="exact")
-        x = seeded_activations(tokens, k, seed=601)
-        q, s = fp8.quantize(x.cuda())
-        rng = np.random.default_rng(5)
-        ids = torch.from_numpy(np.stack([rng.choice(experts, size=top_k, replace=False, p=[0.55, 0.25, 0.1, 0.1]) for _ in range(tokens)])).cuda()
-        plan = parallel.dispatch_masked(q, s, ids, experts, capacity)
-        y = tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), tokens * top_k)
-        back = parallel.combine_masked(y, plan, tokens * top_k)
-        tb.check_status()
-        wq, ws = orc.quantize_fp8_per_token(x)
-        flat = ids.reshape(-1).cpu().numpy()
-        seen = {e: 0 for e in range(experts)}
-        dropped = 0
-        for r, e in enumerate(flat):
-            seen[e] += 1
-            row = back[r].float().cpu()
-            if seen[e] > capacity:
-                assert bool((row == 0).all())
-                dropped += 1
-                continue
-            t = r // top_k
-            want = orc.gemm_dense(wq[t:t + 1], ws[t:t + 1], views[e]["fp8"], float(views[e]["global_scale6"][0]), n, k)[0].float()
-            assert float((row - want).abs().max()) <= float(want.abs().max()) * 2 ** -6
-        assert dropped > 0  # the skewed routing overfills the first expert
+        for step in range(2):
+            step_ids = ids if step == 0 else ids.flip(0).contiguous()
+            want_plan = parallel.dispatch_masked(q, s, step_ids, experts, capacity, placement=placement)
+            plan = exchange.dispatch(q, s, step_ids)
+            assert torch.equal(plan.counts, want_plan.counts)
+            for e in range(experts):
+                lo, c = e * capacity, int(plan.counts[e])
+                assert torch.equal(plan.a.view(torch.uint8)[lo:lo + c], want_plan.a.view(torch.uint8)[lo:lo + c])
+                assert torch.equal(plan.a_scale[lo:lo + c], want_plan.a_scale[lo:lo + c])
+            # experts sit in placed order in both paths
+            order = list(range(experts))
+            weights = ex
+            tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, weights, tb.MaskedRouting(plan.counts), tokens * top_k, out=plan.out)
+            back = exchange.combine(plan)
+            want_y = tb.fp8_nvfp4_grouped_gemm(want_plan.a, want_plan.a_scale, weights, tb.MaskedRouting(want_plan.counts), tokens * top_k)
+            want_back = parallel.combine_masked(want_y, want_plan, tokens * top_k)
+            tb.check_status()
+            assert torch.equal(back, want_back)
+            del order
+        if placement == "contiguous":
+            assert _check_routes(back, ids.flip(0), views, wq, ws, capacity, n, k, top_k) > 0
     finally:
-        if created:
-            dist.destroy_process_group()
+        exchange.close()
