@@ -254,6 +254,65 @@ long long split_scratch_bytes(long long m, long long n, int block_m, int splits)
     return tb::kEpochCells * 4 + tiles * splits * block_m * 128 * 8;
 }
 
+// ---- kernels compiled at run time (tensorbridge/jit) ----------------------------------------------------------------
+// The ahead-of-time instances cover six token tiles and three bridge arrangements.  Any other point of the template
+// (token tiles of 48, 96, 160, 224 ... tokens, 16 bridge warps in two teams, ...) is compiled by NVRTC on the Python side
+// and handed over as a CUfunction; a registered function takes precedence over an ahead-of-time instance of the same key.
+struct KernelKey {
+    int device, block_m, exact, group_scales, bridge_warps, teams;
+    bool operator==(const KernelKey& o) const {
+        return device == o.device && block_m == o.block_m && exact == o.exact && group_scales == o.group_scales &&
+               bridge_warps == o.bridge_warps && teams == o.teams;
+    }
+};
+struct RegisteredKernel { KernelKey key; CUfunction function; };
+std::mutex g_registry_mutex;
+RegisteredKernel g_registry[256];
+int g_registered = 0;
+
+CUfunction find_registered(const KernelKey& key) {
+    std::lock_guard<std::mutex> guard(g_registry_mutex);
+    for (int i = 0; i < g_registered; ++i)
+        if (g_registry[i].key == key) return g_registry[i].function;
+    return nullptr;
+}
+
+bool jit_block_m(int bm) { return bm >= 16 && bm <= 256 && bm % 16 == 0 && (bm < 64 || bm % 32 == 0); }
+
+using LaunchKernelEx = CUresult (*)(const CUlaunchConfig*, CUfunction, void**, void**);
+LaunchKernelEx launch_kernel_ex() {
+    static LaunchKernelEx fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuLaunchKernelEx", &ptr, cudaEnableDefault, &status) != cudaSuccess ||
+            status != cudaDriverEntryPointSuccess) {
+            return static_cast<LaunchKernelEx>(nullptr);
+        }
+        return reinterpret_cast<LaunchKernelEx>(ptr);
+    }();
+    return fn;
+}
+
+int launch_registered(CUfunction function, int threads, cudaStream_t stream, const tb::GemmParams& params, int grid, size_t smem,
+                      bool pdl) {
+    LaunchKernelEx fn = launch_kernel_ex();
+    if (fn == nullptr) return fail(TB_ERR_CUDA, "cuLaunchKernelEx is not available from the driver");
+    CUlaunchConfig cfg = {};
+    cfg.gridDimX = static_cast<unsigned>(grid); cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = static_cast<unsigned>(threads); cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = static_cast<unsigned>(smem);
+    cfg.hStream = stream;
+    CUlaunchAttribute attr[1];
+    attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr[0].value.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    void* args[1] = {const_cast<tb::GemmParams*>(&params)};
+    const CUresult res = fn(&cfg, function, args, nullptr);
+    if (res != CUDA_SUCCESS) return fail(TB_ERR_CUDA, "cuLaunchKernelEx of a run-time compiled kernel failed with %d", static_cast<int>(res));
+    return TB_OK;
+}
+
 int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routing, const tb_config* cfg) {
     if (a == nullptr || cfg == nullptr) return fail(TB_ERR_INVALID, "null arguments");
     if (a->rows < 0 || a->n <= 0 || a->k <= 0) return fail(TB_ERR_INVALID, "bad shape rows=%lld n=%lld k=%lld",
@@ -266,7 +325,9 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
         reinterpret_cast<uintptr_t>(a->scale) % 16 != 0) return fail(TB_ERR_INVALID, "a, weight and scale must be 16-byte aligned");
     if (a->rows > 0x7FFFFFFFll / 2) return fail(TB_ERR_INVALID, "too many rows");
     const int bm = cfg->block_m;
-    if (!valid_block_m(bm)) return fail(TB_ERR_INVALID, "block_m must be 16, 32, 64, 128, 192 or 256, got %d", bm);
+    if (!valid_block_m(bm) && !jit_block_m(bm))
+        return fail(TB_ERR_INVALID, "block_m must be 16, 32, 64, 128, 192 or 256 (or, with a kernel compiled at run time, another "
+                    "multiple of 16 up to 256: of 32 from 64 up), got %d", bm);
     if (cfg->block_n != 128 || cfg->block_k != 128) return fail(TB_ERR_INVALID, "block_n and block_k must be 128");
     if (cfg->ctas_per_sm != 0 && cfg->ctas_per_sm != 1) return fail(TB_ERR_INVALID, "ctas_per_sm must be 1, got %d", cfg->ctas_per_sm);
 
@@ -434,6 +495,10 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     p.static_weights = a->enable_pdl == TB_PDL_STATIC_WEIGHTS ? 1 : 0;
     const int teams = cfg->m_fast_tile_order <= 1 ? 1 : cfg->m_fast_tile_order;
     const bool group = a->group_scales != 0;
+    if (CUfunction jit = find_registered({device, bm, exact ? 1 : 0, group ? 1 : 0, cfg->math_warpgroups * 4, teams}))
+        return launch_registered(jit, tb::gemm_threads(bm, cfg->math_warpgroups * 4), stream, p, grid, smem, pdl);
+    if (!valid_block_m(bm))
+        return fail(TB_ERR_UNSUPPORTED, "no kernel for block_m %d: compile one with tensorbridge.jit.runtime.get_kernel first", bm);
     tb::LaunchFn launch = nullptr;
     if (cfg->math_warpgroups == 2 && teams == 1) launch = tb::launch_w8_t1;
     if (cfg->math_warpgroups == 2 && teams == 2) launch = tb::launch_w8_t2;
@@ -523,7 +588,7 @@ int tb_select_config(const tb_problem* problem, tb_config* config) {
 }
 
 int64_t tb_workspace_bytes(int64_t m, int64_t n, const tb_config* config) {
-    if (config == nullptr || config->use_stream_k <= 1 || m <= 0 || n <= 0 || !valid_block_m(config->block_m)) return 0;
+    if (config == nullptr || config->use_stream_k <= 1 || m <= 0 || n <= 0 || !(valid_block_m(config->block_m) || jit_block_m(config->block_m))) return 0;
     return split_scratch_bytes(m, n, config->block_m, config->use_stream_k);
 }
 
@@ -651,13 +716,38 @@ int tb_bridge_dump(void* stream, const int32_t* weight, const uint8_t* scale, in
     return TB_OK;
 }
 
+int tb_register_kernel(const tb_kernel_key* key, void* function) {
+    if (key == nullptr || function == nullptr) return fail(TB_ERR_INVALID, "null arguments");
+    if (!jit_block_m(key->block_m)) return fail(TB_ERR_INVALID, "block_m %d is no token tile the kernel template takes", key->block_m);
+    if ((key->bridge_warps != 8 && key->bridge_warps != 16) || key->teams < 1 || key->bridge_warps % key->teams != 0 ||
+        (key->bridge_warps / key->teams) % 4 != 0)
+        return fail(TB_ERR_INVALID, "bridge warps %d in %d teams: 8 or 16 warps, teams of 4, 8 or 16 warps", key->bridge_warps, key->teams);
+    if (key->device < 0 || key->device >= 64) return fail(TB_ERR_INVALID, "device %d out of range", key->device);
+    const KernelKey k = {key->device, key->block_m, key->exact ? 1 : 0, key->group_scales ? 1 : 0, key->bridge_warps, key->teams};
+    std::lock_guard<std::mutex> guard(g_registry_mutex);
+    for (int i = 0; i < g_registered; ++i) {
+        if (g_registry[i].key == k) {
+            g_registry[i].function = static_cast<CUfunction>(function);
+            return TB_OK;
+        }
+    }
+    if (g_registered == 256) return fail(TB_ERR_UNSUPPORTED, "the kernel registry holds 256 kernels");
+    g_registry[g_registered++] = {k, static_cast<CUfunction>(function)};
+    return TB_OK;
+}
+
+int tb_registered_kernels(void) {
+    std::lock_guard<std::mutex> guard(g_registry_mutex);
+    return g_registered;
+}
+
 int tb_gemm_dense(void* stream, const tb_gemm_args* args, const tb_config* config) {
     return run_gemm(static_cast<cudaStream_t>(stream), args, nullptr, config);
 }
 
 int tb_gemm_dense_static_scratch(void* stream, const tb_gemm_args* args, const tb_config* config) {
     if (args == nullptr || config == nullptr) return fail(TB_ERR_INVALID, "null arguments");
-    if (!valid_block_m(config->block_m)) return fail(TB_ERR_INVALID, "block_m must be 16, 32, 64, 128, 192 or 256, got %d", config->block_m);
+    if (!valid_block_m(config->block_m) && !jit_block_m(config->block_m)) return fail(TB_ERR_INVALID, "block_m must be a multiple of 16 up to 256, got %d", config->block_m);
     // The splits the launch will really make: never more than K blocks, none with [1,128] scales.
     const int k_blocks = pad128(std::max<long long>(args->k, 1)) / 128;
     const int splits = args->group_scales ? 1 : std::min(std::max(1, static_cast<int>(config->use_stream_k)), k_blocks);

@@ -68,7 +68,8 @@ enum WaitCode : int {
 // half a microsecond of a ten-microsecond launch.
 struct FastDiv {
     uint32_t mul, shr, divisor, pad;
-    __host__ static FastDiv make(uint32_t d) {
+#ifndef __CUDACC_RTC__
+    static FastDiv make(uint32_t d) {
         FastDiv f = {0, 0, d, 0};
         if (d > 1) {
             uint32_t log2_ceil = 0;
@@ -79,6 +80,7 @@ struct FastDiv {
         }
         return f;
     }
+#endif
     __device__ __forceinline__ int div(int n) const {
         return divisor == 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), mul) >> shr);
     }
@@ -180,8 +182,11 @@ __device__ __forceinline__ unsigned long long tb_globaltimer() {
 #define TB_REPORT(slot, value) do { } while (0)
 #endif
 
+// The whole kernel as a device function, so that a translation unit compiled at run time can wrap an instance of it in an
+// entry point with a plain C name (see tensorbridge/jit/codegen.py); `p` must be the kernel's __grid_constant__ parameter
+// itself (the tensor maps are handed to the TMA unit by their address in parameter space).
 template <int BM, bool kExact, bool kGroupScales, int kBridgeWarps, int kBridgeGroups>
-__global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+__device__ __forceinline__ void gemm_body(const GemmParams& p) {
     constexpr int kEpilogueWarps = epilogue_warps(BM);
     constexpr int kColumnGroups = kEpilogueWarps / 4;  // warp w drains lanes 32 * (w % 4) .. +31, columns of group w / 4
     constexpr int kCols = BM / kColumnGroups;          // token columns per epilogue warp
@@ -1038,6 +1043,11 @@ __global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel
             p.status[2] = total_units;
         }
     }
+}
+
+template <int BM, bool kExact, bool kGroupScales, int kBridgeWarps, int kBridgeGroups>
+__global__ void __launch_bounds__(gemm_threads(BM, kBridgeWarps), 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+    gemm_body<BM, kExact, kGroupScales, kBridgeWarps, kBridgeGroups>(p);
 }
 
 }  // namespace tb

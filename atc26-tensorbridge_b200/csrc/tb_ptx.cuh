@@ -3,9 +3,21 @@
 // unwind and report an error instead of hanging.
 #pragma once
 
+#ifdef __CUDACC_RTC__
+// Run-time compilation (NVRTC) has no host headers: the fixed-width integers and an opaque tensor map of the right size
+// and alignment are all the kernels need from them.
+typedef unsigned char uint8_t;
+typedef unsigned short uint16_t;
+typedef unsigned int uint32_t;
+typedef unsigned long long uint64_t;
+typedef unsigned long long uintptr_t;
+struct alignas(64) CUtensorMap_st { unsigned long long opaque[16]; };
+typedef CUtensorMap_st CUtensorMap;
+#else
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#endif
 
 namespace tb {
 

@@ -80,6 +80,12 @@ class PushArgs(ctypes.Structure):
     ]
 
 
+class KernelKey(ctypes.Structure):
+    """`tb_kernel_key`."""
+
+    _fields_ = [(name, ctypes.c_int32) for name in ("device", "block_m", "exact", "group_scales", "bridge_warps", "teams")]
+
+
 # Every symbol include/tensorbridge_b200.h declares: (restype, argtypes).
 SYMBOLS = {
     "tb_last_error": (ctypes.c_char_p, []),
@@ -99,6 +105,8 @@ SYMBOLS = {
                                          ctypes.c_void_p, ctypes.c_void_p]),
     "tb_bridge_dump": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                       ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "tb_register_kernel": (ctypes.c_int, [ctypes.POINTER(KernelKey), ctypes.c_void_p]),
+    "tb_registered_kernels": (ctypes.c_int, []),
     "tb_gemm_dense": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Config)]),
     "tb_gemm_dense_static_scratch": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Config)]),
     "tb_gemm_grouped": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(GemmArgs), ctypes.POINTER(Routing),

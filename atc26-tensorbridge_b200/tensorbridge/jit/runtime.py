@@ -1,8 +1,11 @@
-"""Config selection front end: autotune override -> profile -> the native B200 rule, cached per shape.
+"""Config selection front end (autotune override -> profile -> the native B200 rule, cached per shape) and the kernel
+registry of the JIT.
 
-Keeps the call signature of the reference's `select_config` (`tensorbridge/jit/runtime.py:73-108`).  There is no
-NVRTC step: `get_kernel` / `get_grouped_kernel` of the reference resolve to template instances that already live in
-libtensorbridge_b200.so, so selection is the whole "JIT" front end here.
+Keeps the call signatures of the reference's `select_config` (`tensorbridge/jit/runtime.py:73-108`) and of its
+`get_kernel` / `get_grouped_kernel` (`:162-244`).  A config that names a template point the library was built with
+resolves to that ahead-of-time instance; any other point is generated (`codegen.generate`), compiled with NVRTC
+(`compiler.build`, cached on disk), loaded with the driver API and registered with the library
+(`tb_register_kernel`), after which launches with that config run it.
 """
 from __future__ import annotations
 
@@ -88,3 +91,64 @@ def override_config(m: int, n: int, k: int, config: GemmConfig, device: int, num
     """Serve this shape with `config` from now on (what autotune records)."""
     key = (device, get_num_sms(device), m, n, k, num_experts, layout, bridge, top_k, None, group_scales)
     selected_configs[key] = config
+
+
+# ---- kernels compiled at run time --------------------------------------------------------------------------------
+loaded_kernels: dict[tuple, "LoadedKernel"] = {}
+
+
+class LoadedKernel:
+    """A module loaded on one device and the function registered with the library (the module must stay loaded)."""
+
+    def __init__(self, device: int, point: codegen.KernelPoint, compiled, module, function) -> None:
+        self.device, self.point, self.compiled, self.module, self.function = device, point, compiled, module, function
+
+
+def _driver_check(result, what: str) -> None:
+    from cuda.bindings import driver  # noqa: PLC0415
+
+    if result != driver.CUresult.CUDA_SUCCESS:
+        raise RuntimeError(f"{what} failed: {result}")
+
+
+def get_kernel(n: int, k: int, config: GemmConfig, device: int | None = None, *, bridge: Bridge = "exact",
+               group_scales: bool = False, num_experts: int = 0, layout: codegen.GroupedLayout = "dense") -> "LoadedKernel | None":
+    """Make sure the library can launch `config` on `device`: returns None when the ahead-of-time library holds the
+    template point, else the kernel compiled (or fetched from the disk cache), loaded and registered for it.  Call it
+    outside CUDA-graph capture; launches with `config` need nothing further."""
+    from cuda.bindings import driver  # noqa: PLC0415
+
+    from tensorbridge.jit import compiler  # noqa: PLC0415
+
+    device = torch.cuda.current_device() if device is None else device
+    point = codegen.kernel_point(config, bridge, group_scales)
+    codegen.validate_point(point)
+    if codegen.is_ahead_of_time(point):
+        return None
+    key = (device, point)
+    hit = loaded_kernels.get(key)
+    if hit is not None:
+        return hit
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("get_kernel compiles and loads a module: call it before CUDA graph capture, not during it")
+    compiled = compiler.build(codegen.generate(n, k, config, num_experts, layout, bridge, group_scales=group_scales))
+    with torch.cuda.device(device):
+        torch.cuda.current_stream()  # makes sure the device's primary context is current
+        with open(compiled.cubin_path, "rb") as handle:
+            image = handle.read()
+        result, module = driver.cuModuleLoadData(image)
+        _driver_check(result, "cuModuleLoadData")
+        result, function = driver.cuModuleGetFunction(module, compiled.entry.encode())
+        _driver_check(result, "cuModuleGetFunction")
+        _driver_check(driver.cuFuncSetAttribute(function, driver.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                                227 * 1024)[0], "cuFuncSetAttribute")
+        native_key = _native.KernelKey(device, point.block_m, int(point.exact), int(point.group_scales), point.bridge_warps, point.teams)
+        _native.check(_native.load().tb_register_kernel(ctypes.byref(native_key), ctypes.c_void_p(int(function))))
+    loaded = loaded_kernels[key] = LoadedKernel(device, point, compiled, module, function)
+    return loaded
+
+
+def get_grouped_kernel(n: int, k: int, num_experts: int, layout: codegen.GroupedLayout, config: GemmConfig,
+                       device: int | None = None, *, bridge: Bridge = "exact", group_scales: bool = False) -> "LoadedKernel | None":
+    """`get_kernel` for a grouped call (the kernel is the same template; the layout is a run-time parameter)."""
+    return get_kernel(n, k, config, device, bridge=bridge, group_scales=group_scales, num_experts=num_experts, layout=layout)

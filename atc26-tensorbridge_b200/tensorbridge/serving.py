@@ -7,13 +7,15 @@
 
     moe_forward_*        two grouped GEMMs around activation and quantisation, into caller buffers
 
-Names, arguments and conventions follow the reference's `tensorbridge/serving.py:107-170,356-466,535-703`.  The
-reference's `precompile_prepared` / `autotune_prepared` (NVRTC batch compiles) have no counterpart: kernels here are
-compiled ahead of time.
+Names, arguments and conventions follow the reference's `tensorbridge/serving.py:33-170,173-353,356-703`.
+`precompile_prepared` loads (compiling with NVRTC where the library has no ahead-of-time instance) every kernel the
+selection can pick for the prepared shapes; `autotune_prepared` measures the prepared dense shapes.
 """
 from __future__ import annotations
 
 import dataclasses
+import os
+import warnings
 from collections.abc import Callable, Sequence
 from typing import Literal, TypedDict
 
@@ -22,29 +24,82 @@ import torch
 from tensorbridge import experimental
 from tensorbridge.gemm import (PDL_STATIC_WEIGHTS, ContiguousRouting, IndexedRouting, MaskedRouting, fp8_nvfp4_gemm,
                                fp8_nvfp4_grouped_gemm)
+from tensorbridge.jit import autotune as _autotune
+from tensorbridge.jit import codegen, runtime
 from tensorbridge.jit.codegen import Bridge, GemmConfig
 from tensorbridge.quant import fp8, nvfp4
 
-# Bookkeeping the reference keeps per process: dense shapes prepared, layers prepared, per-stream lock arrays.
-prepared_shapes: set[tuple] = set()
+@dataclasses.dataclass(frozen=True, order=True)
+class DenseShape:
+    """A dense weight shape prepared on `device` (`tensorbridge/serving.py:33-42`)."""
+
+    device: int
+    n: int
+    k: int
+    bridge: Bridge
+    input_quant: fp8.InputQuant = "per_token"
+
+
+@dataclasses.dataclass(frozen=True, order=True)
+class GroupedShape:
+    """One prepared projection of a MoE layer (`tensorbridge/serving.py:44-59`): `top_k` is the layer's routes per
+    token (turns a captured token count into routed rows), `input_top_k` the indexed gather factor of this projection
+    (the down projection reads one row per route)."""
+
+    device: int
+    n: int
+    k: int
+    num_experts: int
+    top_k: int
+    input_top_k: int
+    layout: Literal["indexed", "contiguous", "masked"]
+    bridge: Bridge
+    dispatch_ranks: int
+    num_global_experts: int
+    input_quant: fp8.InputQuant = "per_token"
+
+
+DenseTunedKey = tuple
+
+# Bookkeeping per process, under the reference's names: dense shapes and layers prepared, shapes autotune serves, calls
+# captured without a measured config, grouped projections prepared and tuned.
+prepared_shapes: set[DenseShape | tuple] = set()
 prepared_layers = 0
-prepared_grouped: set[tuple] = set()
+tuned: set[DenseTunedKey] = set()
+captured_untuned = 0
+warned_untuned: set = set()
+prepared_grouped: set[GroupedShape] = set()
+tuned_grouped: set[tuple[GroupedShape, int, int]] = set()
+precompiled_dense: set[tuple[DenseShape, int, int]] = set()
+precompiled_grouped: set[tuple[GroupedShape, int, int]] = set()
 stream_locks: dict[tuple[int, int], torch.Tensor] = {}
 
 
+def autotune_enabled() -> bool:
+    return os.environ.get("TENSORBRIDGE_AUTOTUNE") == "1"
+
+
 def locks_for_current_stream(fallback: torch.Tensor) -> torch.Tensor:
-    """Split-K arrival counters private to the current CUDA stream, so launches on concurrent streams never share
-    counter words.  While the stream is being captured no buffer is allocated: an existing one is reused, else
-    `fallback` (the weight's own array) is returned."""
-    device = fallback.get_device()
-    key = (device, torch.cuda.current_stream(device).cuda_stream)
-    have = stream_locks.get(key)
-    if have is not None:
-        return have
-    if torch.cuda.is_current_stream_capturing():
-        return fallback
-    stream_locks[key] = torch.zeros(1024, dtype=torch.int32, device=fallback.device)
-    return stream_locks[key]
+    """The lock array a launch on the current stream should carry.  The reference hands every stream its own Stream-K
+    counters here (`tensorbridge/serving.py:84-97`); the sm_100a kernels keep no counters in `locks` (the split-K
+    reduction works on tagged partial sums in per-stream scratch, see `tensorbridge.gemm`), so the weight's own array
+    is returned and nothing is allocated."""
+    return fallback
+
+
+def normalize_dense_shape(entry: DenseShape | tuple) -> DenseShape:
+    """`prepared_shapes` entries are `DenseShape`s; older 4-tuples `(device, n, k, bridge)` are accepted."""
+    if isinstance(entry, DenseShape):
+        return entry
+    if len(entry) == 5:
+        return DenseShape(*entry)
+    device, n, k, bridge = entry
+    return DenseShape(device, n, k, bridge, "per_token")
+
+
+def dense_tuned_key(device: int, num_sms: int, n: int, k: int, m: int, bridge: Bridge, input_quant: fp8.InputQuant) -> tuple:
+    base = (device, num_sms, n, k, m, bridge)
+    return base if input_quant == "per_token" else base + (input_quant,)
 
 
 def share_global_scale(weight_scale: torch.Tensor, global_scales: torch.Tensor, shard_sizes: Sequence[int]
@@ -86,7 +141,7 @@ def prepare_linear(weight_packed: torch.Tensor, weight_scale: torch.Tensor, weig
         raise ValueError("fused shards with different global scales need their shard_sizes")
     prepare = experimental.prepare if input_quant == "group_128" else nvfp4.prepare
     weight = prepare(weight_packed, weight_scale, shared.reshape(1), bridge=bridge)
-    prepared_shapes.add((weight.weight.get_device(), *weight.shape, bridge, input_quant))
+    prepared_shapes.add(DenseShape(weight.weight.get_device(), *weight.shape, bridge, input_quant))
     prepared_layers += 1
     return weight
 
@@ -95,13 +150,12 @@ def linear(x: torch.Tensor, weight: nvfp4.NVFP4Weight, output: torch.Tensor, *,
            input_quant: fp8.InputQuant = "per_token") -> None:
     """`output[M, N] = x[M, K] @ dequant(weight).T` for BF16 `x`: quantise to FP8 (`per_token` or `group_128`), then
     the GEMM launched with programmatic dependent launch behind the quantiser."""
-    active = dataclasses.replace(weight, locks=locks_for_current_stream(weight.locks))
     if input_quant == "group_128":
         q, s = fp8.quantize_group_128(x)
-        experimental.fp8_nvfp4_group_quant_gemm(q, s, active, out=output, enable_pdl=PDL_STATIC_WEIGHTS)
+        experimental.fp8_nvfp4_group_quant_gemm(q, s, weight, out=output, enable_pdl=PDL_STATIC_WEIGHTS)
     else:
         q, s = fp8.quantize(x)
-        fp8_nvfp4_gemm(q, s, active, out=output, enable_pdl=PDL_STATIC_WEIGHTS)
+        fp8_nvfp4_gemm(q, s, weight, out=output, enable_pdl=PDL_STATIC_WEIGHTS)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -163,7 +217,7 @@ def prepare_moe(w13_packed: torch.Tensor, w13_scale: torch.Tensor, w13_global_sc
     moe = NVFP4MoE(w13, w2, top_k, num_experts if num_global_experts is None else num_global_experts, dispatch_ranks,
                    layout, configs, gate_up_quant, down_quant, is_gated)
     if configs is None:
-        prepared_grouped.add((w13.weight.get_device(), *w13.shape, *w2.shape, layout, bridge))
+        prepared_grouped.update(moe_grouped_shapes(moe))
     return moe
 
 
@@ -182,29 +236,159 @@ class MoEBuffers(TypedDict):
 ActivationFn = Callable[[torch.Tensor, torch.Tensor], None]
 
 
+def moe_grouped_shapes(moe: NVFP4MoE) -> tuple[GroupedShape, GroupedShape]:
+    """The gate/up and down projections as `GroupedShape`s.  Both see the same routed rows; only an indexed gate/up
+    projection gathers them from token rows (`input_top_k = top_k`)."""
+    device = moe.w13.weight.get_device()
+    shared = dict(device=device, num_experts=moe.w13.shape[0], top_k=moe.top_k, layout=moe.layout,
+                  dispatch_ranks=moe.dispatch_ranks, num_global_experts=moe.num_global_experts)
+    gather = moe.top_k if moe.layout == "indexed" else 1
+    return (GroupedShape(n=moe.w13.shape[1], k=moe.w13.shape[2], input_top_k=gather, bridge=moe.w13.bridge,
+                         input_quant=moe.gate_up_quant, **shared),
+            GroupedShape(n=moe.w2.shape[1], k=moe.w2.shape[2], input_top_k=1, bridge=moe.w2.bridge,
+                         input_quant=moe.down_quant, **shared))
+
+
+def record_grouped_capture(moe: NVFP4MoE, rows: int) -> None:
+    """While a CUDA graph is being captured with autotune on, count (and warn once per shape about) projections whose
+    `rows` were never measured: they keep the rule's config for the life of the graph.  Pinned configs opt out."""
+    global captured_untuned
+    if moe.configs is not None or not autotune_enabled() or not torch.cuda.is_current_stream_capturing():
+        return
+    num_sms = runtime.get_num_sms(moe.w13.weight.get_device())
+    for shape in moe_grouped_shapes(moe):
+        key = (shape, num_sms, rows)
+        if key in tuned_grouped:
+            continue
+        captured_untuned += 1
+        if key not in warned_untuned:
+            warned_untuned.add(key)
+            warnings.warn(f"tensorbridge: grouped GEMM with {rows} routed rows of (N, K, E) = ({shape.n}, {shape.k}, "
+                          f"{shape.num_experts}) captured without autotune; it keeps the selection rule's config", stacklevel=3)
+
+
 def moe_rows(moe: NVFP4MoE, num_routes: int) -> int:
     """Expected routed rows on this rank from the global pre-dispatch `num_routes` (a scheduling hint only)."""
     return (num_routes * moe.w13.shape[0] + moe.num_global_experts - 1) // moe.num_global_experts
 
 
+def moe_post_dispatch_rows(moe: NVFP4MoE, received_tokens: int) -> int:
+    """Expected routed rows on this rank when the dispatch sends each token at most once per rank: a received token
+    has at least one local route, and under uniform routing `top_k * p / (1 - (1 - p)^top_k)` of them in expectation,
+    `p` the local share of the experts.  Bounded by one and `top_k` routes per received token."""
+    if received_tokens <= 0:
+        return 0
+    local = moe.w13.shape[0]
+    if moe.top_k <= 1 or local >= moe.num_global_experts:
+        return received_tokens * moe.top_k
+    share = local / moe.num_global_experts
+    per_token = moe.top_k * share / (1.0 - (1.0 - share) ** moe.top_k)
+    return max(received_tokens, min(received_tokens * moe.top_k, round(received_tokens * per_token)))
+
+
+def moe_block_sizes(moe: NVFP4MoE, rows: int) -> tuple[int, int]:
+    """Token tiles of the gate/up and down projections for `rows` routed rows: what indexed routes must be aligned to.
+    Ask after autotune and before aligning."""
+    if moe.configs is not None:
+        return moe.configs[0].block_m, moe.configs[1].block_m
+    tiles = [runtime.select_config(rows, shape.n, shape.k, shape.num_experts, shape.layout, shape.device, bridge=shape.bridge,
+                                   top_k=shape.input_top_k, group_scales=shape.input_quant == "group_128").block_m
+             for shape in moe_grouped_shapes(moe)]
+    return tiles[0], tiles[1]
+
+
+def precompile_prepared(max_tokens: int) -> int:
+    """Make sure every kernel `select_config` can pick for 1 .. `max_tokens` tokens on the prepared dense and grouped
+    shapes of the current device is loaded, so that no launch meets a compile.  Template points the library was built
+    with cost nothing; the others are compiled with NVRTC (or fetched from the disk cache) and registered.  Returns the
+    number of kernels compiled or loaded by this call (`tensorbridge/serving.py:173-257`)."""
+    if max_tokens < 1:
+        return 0
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("precompile builds kernels: call it before CUDA graph capture, not during it")
+    device = torch.cuda.current_device()
+    num_sms = runtime.get_num_sms(device)
+    # every M up to 256, then every eighth, then the maximum: the sizes decode steps and prefill chunks produce
+    ms = list(range(1, min(max_tokens, 256) + 1)) + list(range(264, max_tokens + 1, 8))
+    if ms[-1] != max_tokens:
+        ms.append(max_tokens)
+    before = len(runtime.loaded_kernels)
+    for entry in sorted({normalize_dense_shape(e) for e in prepared_shapes}):
+        if entry.device != device or (entry, num_sms, max_tokens) in precompiled_dense:
+            continue
+        group = entry.input_quant == "group_128"
+        for config in dict.fromkeys(runtime.select_config(m, entry.n, entry.k, device=device, bridge=entry.bridge, group_scales=group)
+                                    for m in ms):
+            runtime.get_kernel(entry.n, entry.k, config, device, bridge=entry.bridge, group_scales=group)
+        precompiled_dense.add((entry, num_sms, max_tokens))
+    for shape in sorted(prepared_grouped):
+        if shape.device != device or (shape, num_sms, max_tokens) in precompiled_grouped:
+            continue
+        group = shape.input_quant == "group_128"
+        rows = sorted({(shape.dispatch_ranks * m * shape.top_k * shape.num_experts + shape.num_global_experts - 1) // shape.num_global_experts
+                       for m in ms})
+        for config in dict.fromkeys(runtime.select_config(r, shape.n, shape.k, shape.num_experts, shape.layout, device,
+                                                          bridge=shape.bridge, top_k=shape.input_top_k, group_scales=group) for r in rows):
+            runtime.get_grouped_kernel(shape.n, shape.k, shape.num_experts, shape.layout, config, device, bridge=shape.bridge,
+                                       group_scales=group)
+        precompiled_grouped.add((shape, num_sms, max_tokens))
+    return len(runtime.loaded_kernels) - before
+
+
+def autotune_prepared(ms: Sequence[int]) -> None:
+    """With `TENSORBRIDGE_AUTOTUNE=1`: measure every dense shape prepared on the current device at the token counts
+    `ms` (the sizes a CUDA graph will capture) on seeded random weights and activations of that shape, and serve the
+    winners from then on.  Call it before capture; sizes already measured are skipped
+    (`tensorbridge/serving.py:269-353`; grouped projections are measured by `autotune_grouped` with real routing)."""
+    if not autotune_enabled() or not ms:
+        return
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("autotune times kernels: call it before CUDA graph capture, not during it")
+    device = torch.cuda.current_device()
+    num_sms = runtime.get_num_sms(device)
+    dev = torch.device("cuda", device)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    for entry in sorted({normalize_dense_shape(e) for e in prepared_shapes}):
+        if entry.device != device:
+            continue
+        todo = [m for m in ms if m > 0 and dense_tuned_key(device, num_sms, entry.n, entry.k, m, entry.bridge, entry.input_quant) not in tuned]
+        if not todo:
+            continue
+        group = entry.input_quant == "group_128"
+        checkpoint = nvfp4.quantize((torch.randn((entry.n, entry.k), generator=gen, device=dev) * 0.02).bfloat16())
+        weight = (experimental.prepare if group else nvfp4.prepare)(*checkpoint, bridge=entry.bridge)
+        for m in todo:
+            x = torch.randn((m, entry.k), generator=gen, device=dev).bfloat16()
+            a, a_scale = (fp8.quantize_group_128 if group else fp8.quantize)(x)
+            _autotune.autotune(a, a_scale.contiguous() if group else a_scale, weight, group_scales=group)
+            tuned.add(dense_tuned_key(device, num_sms, entry.n, entry.k, m, entry.bridge, entry.input_quant))
+
+
 def moe_buffer_specs(moe: NVFP4MoE, num_tokens: int, *, unfused_activation: bool = False
                      ) -> dict[str, tuple[tuple[int, ...], torch.dtype]]:
-    """Shapes and dtypes of the buffers `moe_forward_*` needs for `num_tokens` tokens seen by this rank, with room
-    for every route (`tensorbridge/serving.py:535-554`)."""
-    rows = num_tokens * (moe.w13.shape[0] if moe.layout == "masked" else moe.top_k)
-    input_rows = num_tokens if moe.layout == "indexed" else rows
-    _, w13_channels, _ = moe.w13.shape
-    _, hidden, intermediate = moe.w2.shape
-    specs: dict[str, tuple[tuple[int, ...], torch.dtype]] = {
-        "input": ((input_rows, hidden), torch.float8_e4m3fn),
-        "input_scale": ((input_rows, hidden // 128 if moe.gate_up_quant == "group_128" else 1), torch.float32),
-        "gate_up": ((rows, w13_channels), torch.bfloat16),
-        "intermediate": ((rows, intermediate), torch.float8_e4m3fn),
-        "intermediate_scale": ((rows, intermediate // 128 if moe.down_quant == "group_128" else 1), torch.float32),
-        "output": ((rows, hidden), torch.bfloat16),
+    """Shapes and dtypes of the buffers `moe_forward_*` needs for `num_tokens` tokens seen by this rank, sized for the
+    worst routing.  Rows follow from the layout: a masked layer gives every local expert a block of `num_tokens` rows,
+    the other two hold one row per route (`num_tokens * top_k`); only an indexed layer keeps its input per token, since
+    its gate/up projection gathers rows by route.  Scale columns are one per row, or one per 128 input columns of the
+    projection that reads them."""
+    experts, gate_up_channels, hidden = moe.w13.shape
+    intermediate = moe.w2.shape[2]
+    routed = num_tokens * (experts if moe.layout == "masked" else moe.top_k)
+    tokens_in = num_tokens if moe.layout == "indexed" else routed
+
+    def scale_columns(width: int, quant: str) -> int:
+        return width // 128 if quant == "group_128" else 1
+
+    specs = {
+        "input": ((tokens_in, hidden), torch.float8_e4m3fn),
+        "input_scale": ((tokens_in, scale_columns(hidden, moe.gate_up_quant)), torch.float32),
+        "gate_up": ((routed, gate_up_channels), torch.bfloat16),
+        "intermediate": ((routed, intermediate), torch.float8_e4m3fn),
+        "intermediate_scale": ((routed, scale_columns(intermediate, moe.down_quant)), torch.float32),
+        "output": ((routed, moe.w2.shape[1]), torch.bfloat16),
     }
     if unfused_activation:
-        specs["activated"] = ((rows, intermediate), torch.bfloat16)
+        specs["activated"] = ((routed, intermediate), torch.bfloat16)
     return specs
 
 

@@ -39,7 +39,8 @@ enum { TB_QUANT_PER_TOKEN = 0, TB_QUANT_GROUP_128 = 1 };
 
 /* The nine-field kernel configuration, in the wire order of tensorbridge/jit/codegen.py:40-49 and
  * tensorbridge/csrc/heuristics/config.hpp:28-55.  On sm_100a the fields mean:
- *   block_m            token tile (UMMA N): 16, 32, 64, 128 or 256
+ *   block_m            token tile (UMMA N): 16, 32, 64, 128, 192 or 256 ahead of time; other multiples of 16 (of 32 from
+ *                      64 up) once tb_register_kernel has a kernel for them
  *   num_stages         depth of the weight ring (codes + scales, 9 KB a stage), rounded down to a multiple of the
  *                      bridge teams; the token ring takes what is left of shared memory, at most 8 stages
  *   use_stream_k       number of deterministic K splits of a dense GEMM (0 or 1 = none)
@@ -158,6 +159,26 @@ int tb_prepare_weight(void* stream, const uint8_t* packed, const uint8_t* scale,
  * tensorbridge/include/tensorbridge/dequant/fpma.cuh:28-53. */
 int tb_bridge_dump(void* stream, const int32_t* weight, const uint8_t* scale, int64_t num_experts, int64_t n_pad,
                    int64_t k_pad, int bridge, int group_scale_layout, uint8_t* fp8_out);
+
+/* A kernel compiled at run time (NVRTC) for a point of the kernel template the library has no ahead-of-time instance
+ * of -- token tiles of 48, 96, 160, 224 ... tokens, other bridge arrangements.  `function` is a CUfunction of a loaded
+ * module whose entry point wraps tb::gemm_body<block_m, exact, group_scales, bridge_warps, teams> (csrc/tb_gemm.cuh) and
+ * whose maximum dynamic shared memory has been raised to 227 KB; it serves every later launch on `device` whose config
+ * asks for that point.  Replaces register_device_kernel / get_kernel of the reference's launcher
+ * (tensorbridge/csrc/launcher/launcher.cpp:208-239, tensorbridge/jit/runtime.py:162-244). */
+typedef struct tb_kernel_key {
+    int32_t device;
+    int32_t block_m;       /* multiple of 16 up to 256 (of 32 from 64 up) */
+    int32_t exact;         /* bridge: 1 exact, 0 fpma */
+    int32_t group_scales;
+    int32_t bridge_warps;  /* 8 or 16 */
+    int32_t teams;         /* teams of 4, 8 or 16 warps */
+} tb_kernel_key;
+
+int tb_register_kernel(const tb_kernel_key* key, void* function);
+
+/* Number of kernels registered so far. */
+int tb_registered_kernels(void);
 
 #define TB_PDL_STATIC_WEIGHTS 2
 
