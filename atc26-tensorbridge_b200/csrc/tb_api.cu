@@ -175,9 +175,9 @@ int rule(const tb_problem& pr, tb_config* cfg) {
                                                         (long long)pr.m, (long long)pr.n, (long long)pr.k);
     const int sms = pr.num_sms > 0 ? pr.num_sms : kB200Sms;
     const int n_tiles = pad128(pr.n) / 128, k_blocks = pad128(pr.k) / 128;
-    // Group scales keep one accumulator per column in registers; the 128-token instance exists but spills and measured
-    // slower than 64 (config 4: 308 against 406 TFLOP/s), so the rule stops at 64.
-    const int max_bm = pr.group_scales ? 64 : 256;
+    // Group scales keep one FP32 total per column in registers: 64 a lane on the 128-token tile, which the instance
+    // affords by moving registers from its bridge warps to its epilogue warps (tb_gemm.cuh, rebalances_registers).
+    const int max_bm = pr.group_scales ? 128 : 256;
     int bm;
     int splits = 1;
     if (pr.layout == TB_LAYOUT_DENSE) {
@@ -504,8 +504,9 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     if (cfg->math_warpgroups == 2 && teams == 2) launch = tb::launch_w8_t2;
     if (cfg->math_warpgroups == 4 && teams == 4) launch = tb::launch_w16_t4;
     if (launch == nullptr)
-        return fail(TB_ERR_INVALID, "unsupported bridge warps / teams: math_warpgroups %d, m_fast_tile_order %d",
-                    cfg->math_warpgroups, cfg->m_fast_tile_order);
+        return fail(TB_ERR_UNSUPPORTED, "no kernel for %d bridge warps in %d teams (math_warpgroups %d, m_fast_tile_order %d): the "
+                    "library holds 8 warps in 1 or 2 teams and 16 in 4; compile one with tensorbridge.jit.runtime.get_kernel first",
+                    cfg->math_warpgroups * 4, teams, cfg->math_warpgroups, cfg->m_fast_tile_order);
     const int rc = launch(bm, exact, group, stream, p, grid, smem, pdl);
     if (rc == tb::kLaunchUnsupported)
         return fail(TB_ERR_UNSUPPORTED, "no kernel for block_m %d%s", bm, group ? " with group scales" : "");

@@ -144,6 +144,20 @@ __host__ __device__ constexpr int max_bridged_stages(int bm, bool group_scales) 
                ? kMaxBridgedStages : (kTmemCols - acc_sets(bm, group_scales) * bm) / kTileCols;
 }
 
+// Register shares with [1,128] activation scales on the 128-token tile: every epilogue lane keeps 64 FP32 totals live
+// across the K loop, which does not fit the even share of the register file, while the bridge warps need little.  The
+// two bridge warpgroups give registers back (setmaxnreg.dec) and the two epilogue warpgroups take them
+// (setmaxnreg.inc).  inc waits until the pool holds enough, so the sum of the two targets must not exceed twice the
+// kernel's own count: the host checks that count before it launches such an instance.
+constexpr int kRebalancedBridgeRegs = 64;
+constexpr int kRebalancedEpilogueRegs = 128;
+__host__ __device__ constexpr bool rebalances_registers(int bm, bool group_scales, int bridge_warps) {
+    return group_scales && bm == 128 && bridge_warps == 8;
+}
+__host__ __device__ constexpr int min_kernel_registers(int bm, bool group_scales, int bridge_warps) {
+    return rebalances_registers(bm, group_scales, bridge_warps) ? (kRebalancedBridgeRegs + kRebalancedEpilogueRegs) / 2 : 0;
+}
+
 struct SmemLayout {
     uint32_t tokens, token_stage, weights, weight_stage, barriers, misc, ids, epi, transpose, prefix, total;
 };
@@ -572,6 +586,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         }
     } else if (warp >= kEpilogueWarps) {
         // =========================== bridge ===========================
+        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_dec<kRebalancedBridgeRegs>();
         // Thread bt of a team owns vectors bt, bt + kTeamThreads, ... of its 128 x 128 block (layout in tb_bridge.cuh).
         const int team = (warp - kEpilogueWarps) / kGroupWarps;
         const int first = team;  // its first K block; then every kTurns-th
@@ -641,6 +656,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         if (warp == kEpilogueWarps && lane == 0) { TB_REPORT(4, TB_CLOCK() - loop_begin); TB_REPORT(5, waited_raw); TB_REPORT(6, waited_empty); }
     } else {
         // =========================== epilogue ===========================
+        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_inc<kRebalancedEpilogueRegs>();
         const int quad = warp & 3, cgroup = warp >> 2;
         const int col0 = cgroup * kCols;          // first token column of this warp
         const int n_local = quad * 32 + lane;     // TMEM lane = channel within a 128-channel tile
@@ -773,14 +789,12 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         tmem_ld_16(lane_base + acc * BM + col0 + c * 32 + 16, v[1]);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int j4 = 0; j4 < 8; ++j4) {
+                        for (int j4 = 0; j4 < 8; ++j4) {  // two packed FP32 multiply-adds per four columns
                             const float4 s4 = *reinterpret_cast<const float4*>(my_scale + c * 32 + j4 * 4);
                             const uint32_t* vv = &v[j4 >> 2][(j4 & 3) * 4];
                             float* tt = &total[c * 32 + j4 * 4];
-                            tt[0] = fmaf(__uint_as_float(vv[0]), s4.x, tt[0]);
-                            tt[1] = fmaf(__uint_as_float(vv[1]), s4.y, tt[1]);
-                            tt[2] = fmaf(__uint_as_float(vv[2]), s4.z, tt[2]);
-                            tt[3] = fmaf(__uint_as_float(vv[3]), s4.w, tt[3]);
+                            fma2(tt[0], tt[1], __uint_as_float(vv[0]), __uint_as_float(vv[1]), s4.x, s4.y);
+                            fma2(tt[2], tt[3], __uint_as_float(vv[2]), __uint_as_float(vv[3]), s4.z, s4.w);
                         }
                     }
                     if constexpr (kCols % 32 != 0) {  // a trailing 16-column chunk (token tile 16)

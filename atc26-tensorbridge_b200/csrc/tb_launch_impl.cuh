@@ -22,6 +22,13 @@ int launch_instance(cudaStream_t stream, const GemmParams& params, int grid, siz
         if (!configured[device]) {
             err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemOptIn);
             if (err != cudaSuccess) return static_cast<int>(err);
+            // An instance whose warpgroups trade registers must own enough of them, or its epilogue would wait for ever.
+            if (min_kernel_registers(BM, kGroupScales, kWarps) > 0) {
+                cudaFuncAttributes attributes;
+                err = cudaFuncGetAttributes(&attributes, kernel);
+                if (err != cudaSuccess) return static_cast<int>(err);
+                if (attributes.numRegs < min_kernel_registers(BM, kGroupScales, kWarps)) return kLaunchUnsupported;
+            }
             configured[device] = true;
         }
     }

@@ -217,6 +217,23 @@ __device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint4& a, const 
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- register shares ----------------------------------------------------------------------------------
+// Whole-warpgroup calls (four consecutive warps starting at a multiple of four, all of their threads).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs)); }
+
+// (x, y) += (a, b) * (s, t) as one packed FP32 instruction.
+__device__ __forceinline__ void fma2(float& x, float& y, float a, float b, float s, float t) {
+    asm("{\n\t.reg .b64 acc, lhs, rhs;\n\t"
+        "mov.b64 acc, {%0, %1};\n\tmov.b64 lhs, {%2, %3};\n\tmov.b64 rhs, {%4, %5};\n\t"
+        "fma.rn.f32x2 acc, lhs, rhs, acc;\n\t"
+        "mov.b64 {%0, %1}, acc;\n\t}\n"
+        : "+f"(x), "+f"(y)
+        : "f"(a), "f"(b), "f"(s), "f"(t));
+}
+
 // ---- misc --------------------------------------------------------------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

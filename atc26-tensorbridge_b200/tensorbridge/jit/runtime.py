@@ -142,6 +142,13 @@ def get_kernel(n: int, k: int, config: GemmConfig, device: int | None = None, *,
         _driver_check(result, "cuModuleGetFunction")
         _driver_check(driver.cuFuncSetAttribute(function, driver.CUfunction_attribute.CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
                                                 227 * 1024)[0], "cuFuncSetAttribute")
+        if point.group_scales and point.block_m == 128 and point.bridge_warps == 8:
+            # this instance moves registers from its bridge warpgroups to its epilogue warpgroups (64 and 128 a thread):
+            # with fewer than 96 of its own the epilogue's request could never be met
+            result, registers = driver.cuFuncGetAttribute(driver.CUfunction_attribute.CU_FUNC_ATTRIBUTE_NUM_REGS, function)
+            _driver_check(result, "cuFuncGetAttribute")
+            if registers < 96:
+                raise RuntimeError(f"{compiled.entry} was compiled with {registers} registers a thread; its register hand-over needs 96")
         native_key = _native.KernelKey(device, point.block_m, int(point.exact), int(point.group_scales), point.bridge_warps, point.teams)
         _native.check(_native.load().tb_register_kernel(ctypes.byref(native_key), ctypes.c_void_p(int(function))))
     loaded = loaded_kernels[key] = LoadedKernel(device, point, compiled, module, function)

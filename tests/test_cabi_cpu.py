@@ -45,7 +45,7 @@ def test_rule_small_m_splits_k_and_large_m_does_not(lib):
     assert runtime.rule_config(16, 6144, 7168, 148, split_k_override=0).use_stream_k == 0
     grouped = runtime.rule_config(4096, 4096, 7168, 148, 32, "masked")
     assert grouped.use_stream_k == 0 and grouped.block_m == 256  # twice the mean of 128 rows per expert
-    assert runtime.rule_config(16384, 7168, 2048, 148, 128, "contiguous", True).block_m <= 64
+    assert runtime.rule_config(16384, 7168, 2048, 148, 128, "contiguous", True).block_m == 128  # [1,128] scales: up to 128 tokens
     for m in (1, 300, 5000):
         cfg = runtime.rule_config(m, 6144, 7168, 148)
         assert 2 <= cfg.num_stages <= 16 and cfg.block_n == 128 and cfg.block_k == 128
