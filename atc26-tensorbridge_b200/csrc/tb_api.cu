@@ -382,6 +382,19 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     p.num_experts = experts;
     p.top_k = routing != nullptr && layout == TB_LAYOUT_INDEXED ? routing->top_k : 1;
     p.status = a->status;
+    if (a->row_target != nullptr) {
+        if (layout != TB_LAYOUT_MASKED && layout != TB_LAYOUT_CONTIGUOUS)
+            return fail(TB_ERR_INVALID, "row_target (output rows scattered to the ranks' buffers) goes with masked or contiguous routing");
+        if (a->peer_out == nullptr || a->peer_count < 1 || a->peer_count > tb::kMaxOutputPeers)
+            return fail(TB_ERR_INVALID, "row_target needs peer_out with 1..%d pointers", tb::kMaxOutputPeers);
+        if (a->n % 8 != 0) return fail(TB_ERR_INVALID, "scattered output rows need N to be a multiple of 8");
+        p.row_target = a->row_target;
+        for (int i = 0; i < a->peer_count; ++i) {
+            if (a->peer_out[i] == nullptr || reinterpret_cast<uintptr_t>(a->peer_out[i]) % 16 != 0)
+                return fail(TB_ERR_INVALID, "peer_out[%d] must be a 16-byte aligned device pointer", i);
+            p.peer_out[i] = static_cast<__nv_bfloat16*>(a->peer_out[i]);
+        }
+    }
     // Wait budget in SM cycles: the default is about a second; `wait_us` counts at 2 GHz (the clock tops out below).
     p.wait_cycles = a->wait_us > 0 ? static_cast<long long>(a->wait_us) * 2000 : tb::kWaitCycles;
     if (a->only_split < 0) return fail(TB_ERR_INVALID, "only_split must not be negative");

@@ -182,6 +182,14 @@ int tb_ep_push(void* stream, const tb_ep_push_args* a) {
     tb::PushParams p = {};
     if (int rc = fill_peers(&p.a, a->peer_a, a->world, "activation")) return rc;
     if (int rc = fill_peers(&p.a_scale, a->peer_a_scale, a->world, "scale")) return rc;
+    if (a->peer_row_target != nullptr) {
+        if (a->routes >= (1 << 26) || a->world > 32) return tb::set_last_error(TB_ERR_INVALID, "row targets hold 26 bits of route and 5 of rank");
+        if (int rc = fill_peers(&p.row_target, a->peer_row_target, a->world, "row target")) return rc;
+        if (a->out != nullptr && (a->out_row_bytes <= 0 || a->out_row_bytes % 16 != 0))
+            return tb::set_last_error(TB_ERR_INVALID, "out_row_bytes must be a positive multiple of 16");
+        p.out = static_cast<uint8_t*>(a->out);
+        p.out_row_bytes = static_cast<int>(a->out_row_bytes);
+    }
     p.ids = a->topk_ids; p.x = static_cast<const uint8_t*>(a->x); p.scale = a->scale; p.route_rank = a->route_rank;
     p.all_counts = a->all_counts; p.dest_row = a->dest_row; p.counts = a->counts; p.routes = a->routes; p.ids_int64 = a->ids_int64;
     p.top_k = a->top_k; p.num_experts = a->num_experts; p.world = a->world; p.rank = a->rank; p.interleaved = a->interleaved;

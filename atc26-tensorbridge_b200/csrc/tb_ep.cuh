@@ -302,6 +302,9 @@ struct PushParams {
     int* dest_row;             // [routes] out: row in the owner's masked buffer, -1 = not sent
     int* counts;               // [E / world] out: rows of this rank's own experts, clamped to the capacity
     PeerPointers a, a_scale;   // every rank's masked buffers
+    PeerPointers row_target;   // optional (ptr[0] != nullptr): every rank's int32 [E / world * capacity] table
+    uint8_t* out;              // optional: this rank's route buffer, rows of routes that are not sent are cleared
+    int out_row_bytes;
     long long routes;
     int ids_int64, top_k, num_experts, world, rank, interleaved, capacity, width, groups;
 };
@@ -330,7 +333,15 @@ ep_push_kernel(const PushParams p) {
             if (slot < p.capacity) row = (placed - owner * e_local) * p.capacity + slot;
         }
         if (lane == 0) p.dest_row[r] = row;
-        if (row < 0) continue;
+        if (row < 0) {
+            if (p.out != nullptr) {
+                uint4* cleared = reinterpret_cast<uint4*>(p.out + r * p.out_row_bytes);
+                for (int v = lane; v < p.out_row_bytes / 16; v += 32) cleared[v] = make_uint4(0, 0, 0, 0);
+            }
+            continue;
+        }
+        if (lane == 0 && p.row_target.ptr[0] != nullptr)
+            static_cast<int*>(p.row_target.ptr[owner])[row] = (p.rank << 26) | static_cast<int>(r);
         const long long token = r / p.top_k;
         const uint4* src = reinterpret_cast<const uint4*>(p.x + token * p.width);
         uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.a.ptr[owner]) + static_cast<long long>(row) * p.width);

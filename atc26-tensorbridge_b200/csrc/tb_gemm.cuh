@@ -44,6 +44,7 @@ constexpr int kTileCols = 32;  // tensor-memory columns of one bridged FP8 tile:
 constexpr int kTmemCols = 512;
 constexpr int kMaxAccSets = 8;
 constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K workspace: [0] launch sequence, [1] CTAs arrived
+constexpr int kMaxOutputPeers = 16;   // ranks whose buffers an epilogue can scatter to
 constexpr int kMaxSplitTiles = 128;  // output tiles of a K-split launch: the tile index takes 7 bits of a tag
 constexpr int kTransposeBytes = 16 * 32 * 2;  // an epilogue warp's 16-column chunk as BF16 [token][channel]
 constexpr int kBarrierBytes = 832;     // 4 * 16 + 2 * 8 + 2 * 8 + 1 barriers of 8 bytes, padded
@@ -115,6 +116,11 @@ struct alignas(64) GemmParams {
     const int* num_tokens_padded;
     long long sorted_capacity;
     int* status;
+    // Grouped launches of an expert-parallel step: row r of `a` belongs to route row_target[r] & 0x3FFFFFF of rank
+    // row_target[r] >> 26 (-1: nobody's), and its output row goes straight into that rank's buffer peer_out[rank] (plain
+    // stores over NVLink, row stride n) instead of `d`.  Null for every other launch.
+    const int* row_target;
+    __nv_bfloat16* peer_out[kMaxOutputPeers];
     FastDiv div_splits, div_n_tiles;  // dense unit -> (tile, split); tile or token block -> (token block, channel tile)
     long long wait_cycles;  // budget of every bounded wait
     int only_split;         // test hook: s + 1 runs only the units of K split s (0 = all)
@@ -251,6 +257,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
 
     const bool indexed = p.layout == kIndexed;
     const bool gather = indexed && p.a_gathered == 0;  // rows fetched one by one inside the kernel
+    const bool routed = indexed || p.row_target != nullptr;  // output rows come from a table, not from the tile's position
 
     // ---- set-up (overlaps the previous kernel under PDL: no global reads yet) ----
     if (threadIdx.x == 0) TB_PHASE(0);
@@ -703,6 +710,11 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             const bool partial = !kGroupScales && p.layout == kDense && p.splits > 1;
             const uint32_t tag = (static_cast<uint32_t>(t.tile) << 25) | ((launch_seq + 1u) & 0x1FFFFFFu);
             const int cols_valid = indexed ? kCols : max(0, min(kCols, t.rows_valid - col0));  // live columns of this warp
+            // First element of a staged output row: a row of `d`, or (expert-parallel scatter) of the owning rank's buffer.
+            auto out_row_ptr = [&](int row) -> __nv_bfloat16* {
+                if (p.row_target == nullptr) return p.d + static_cast<long long>(row) * p.n;
+                return p.peer_out[row >> 26] + static_cast<long long>(row & 0x3FFFFFF) * p.n;
+            };
             // Writes the turned chunk c to the staged output rows of its columns: lane -> row lane / 4 (and + 8) of the
             // chunk, 8-channel word lane % 4 of the row.
             auto flush_turned = [&](int c) {
@@ -714,7 +726,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 for (int h = 0; h < 2; ++h) {
                     const int row = my_row[c * 16 + h * 8 + tok];
                     const uint4 word = *reinterpret_cast<const uint4*>(turned + (h * 8 + tok) * 32 + part * 8);
-                    if (nv < p.n && row >= 0) *reinterpret_cast<uint4*>(p.d + static_cast<long long>(row) * p.n + nv) = word;
+                    if (nv < p.n && row >= 0) *reinterpret_cast<uint4*>(out_row_ptr(row) + nv) = word;
                 }
                 __syncwarp();
             };
@@ -733,6 +745,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         if (id >= 0 && id < route_limit) { in_row = id / p.top_k; out_row = id; }
                     } else if (i < t.rows_valid) {
                         in_row = out_row = t.row0 + i;
+                        if (p.row_target != nullptr) out_row = p.row_target[in_row];
                     }
                     my_row[c] = static_cast<int>(out_row);
                     if constexpr (!kGroupScales) my_scale[c] = in_row >= 0 ? p.a_scale[in_row * p.a_scale_stride_m] * gs : 0.f;
@@ -830,7 +843,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
 #pragma unroll
                     for (int c = 0; c < kCols; ++c) {
                         const int out_row = my_row[c];
-                        if (out_row >= 0 && n_ok) p.d[static_cast<long long>(out_row) * p.n + n] = __float2bfloat16_rn(total[c] * gs);
+                        if (out_row >= 0 && n_ok) out_row_ptr(out_row)[n] = __float2bfloat16_rn(total[c] * gs);
                     }
                 }
             } else {
@@ -840,7 +853,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 const int n = t.nt * 128 + n_local;
                 const bool n_ok = n < p.n;
                 const bool wide_stores = wide();
-                if (!partial && !indexed && wide_stores) {
+                if (!partial && !routed && wide_stores) {
                     // Rows of the tile are consecutive rows of the output: one pointer, a fixed step per column.
                     __nv_bfloat16* const turned = turned_chunk();
                     const int tok = lane >> 2, part = lane & 3;
@@ -870,7 +883,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         }
                         __syncwarp();
                     }
-                } else if (!partial && !indexed) {
+                } else if (!partial && !routed) {
                     // The same rows, any channel count or alignment: one pointer, a fixed step per column.
                     __nv_bfloat16* const out0 = p.d + static_cast<long long>(t.row0 + col0) * p.n + n;
                     const long long step = p.n;
@@ -924,8 +937,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 if (rv[e] >= 0 && n_ok)
-                                    p.d[static_cast<long long>(rv[e]) * p.n + n] =
-                                        __float2bfloat16_rn(__uint_as_float(v[j4 * 4 + e]) * sv[e]);
+                                    out_row_ptr(rv[e])[n] = __float2bfloat16_rn(__uint_as_float(v[j4 * 4 + e]) * sv[e]);
                             }
                         }
                     }

@@ -11,6 +11,7 @@ from tensorbridge.gemm import (
     ContiguousRouting,
     IndexedRouting,
     MaskedRouting,
+    PeerScatter,
     Routing,
     fp8_nvfp4_gemm,
     fp8_nvfp4_grouped_gemm,
@@ -23,6 +24,6 @@ from tensorbridge.quant.nvfp4 import NVFP4Experts, NVFP4Weight
 
 __all__ = [
     "Bridge", "ContiguousRouting", "GemmConfig", "IndexedRouting", "MaskedRouting", "NVFP4Experts", "NVFP4Linear",
-    "NVFP4Weight", "PDL_STATIC_WEIGHTS", "Routing", "autotune", "autotune_grouped", "check_status", "fp8_nvfp4_gemm",
+    "NVFP4Weight", "PDL_STATIC_WEIGHTS", "PeerScatter", "Routing", "autotune", "autotune_grouped", "check_status", "fp8_nvfp4_gemm",
     "fp8_nvfp4_grouped_gemm", "select_config",
 ]

@@ -44,7 +44,8 @@ class GemmArgs(ctypes.Structure):
         ("workspace_bytes", ctypes.c_int64), ("d", ctypes.c_void_p), ("rows", ctypes.c_int64), ("n", ctypes.c_int64),
         ("k", ctypes.c_int64), ("bridge", ctypes.c_int32), ("group_scales", ctypes.c_int32),
         ("enable_pdl", ctypes.c_int32), ("num_sms", ctypes.c_int32), ("status", ctypes.c_void_p),
-        ("wait_us", ctypes.c_int32), ("only_split", ctypes.c_int32),
+        ("wait_us", ctypes.c_int32), ("only_split", ctypes.c_int32), ("row_target", ctypes.c_void_p),
+        ("peer_out", ctypes.POINTER(ctypes.c_void_p)), ("peer_count", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
 
 
@@ -76,7 +77,8 @@ class PushArgs(ctypes.Structure):
         ("route_rank", ctypes.c_void_p), ("all_counts", ctypes.c_void_p), ("num_experts", ctypes.c_int32),
         ("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("interleaved", ctypes.c_int32), ("capacity", ctypes.c_int32),
         ("reserved", ctypes.c_int32), ("peer_a", ctypes.POINTER(ctypes.c_void_p)), ("peer_a_scale", ctypes.POINTER(ctypes.c_void_p)),
-        ("dest_row", ctypes.c_void_p), ("counts", ctypes.c_void_p),
+        ("dest_row", ctypes.c_void_p), ("counts", ctypes.c_void_p), ("peer_row_target", ctypes.POINTER(ctypes.c_void_p)),
+        ("out", ctypes.c_void_p), ("out_row_bytes", ctypes.c_int64),
     ]
 
 

@@ -44,6 +44,18 @@ class MaskedRouting:
 
 Routing = IndexedRouting | ContiguousRouting | MaskedRouting
 
+
+@dataclasses.dataclass(frozen=True)
+class PeerScatter:
+    """Where a masked or contiguous grouped launch of an expert-parallel step sends its output rows: `row_target` int32
+    `[rows]` names, for every row of `a`, the rank and route it belongs to (`rank << 26 | route`, -1 = nobody's), and
+    `peer_out` holds every rank's BF16 route buffer as mapped into this process.  The epilogue stores each row straight
+    into the owner's buffer, so no combine pass follows the GEMM (`tensorbridge.parallel.PeerMaskedExchange` builds one)."""
+
+    row_target: torch.Tensor
+    peer_out: object  # ctypes array of device pointers, one per rank
+    world: int
+
 # FP32 split-K scratch per (device, stream): distinct streams never share partial sums.
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 # Buffers that were replaced by larger ones.  A CUDA graph captured earlier on the stream still launches with the old
@@ -189,7 +201,7 @@ def _relaunch(call: _Call, device: torch.device) -> None:
 
 
 def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, rows, n, k, bridge, group_scales,
-            enable_pdl, config, routing_struct, call: _Call | None = None) -> _Call:
+            enable_pdl, config, routing_struct, call: _Call | None = None, scatter: PeerScatter | None = None) -> _Call:
     """One launch through the C ABI.  `call` carries the structs of an earlier launch with the same weight, shape,
     config and mode: only the activation, scale, output, workspace and status pointers are patched."""
     device = a.device
@@ -205,6 +217,8 @@ def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, ro
     args = call.args
     args.a, args.a_scale, args.d = a.data_ptr(), a_scale.data_ptr(), out.data_ptr()
     args.a_scale_stride_m, args.a_scale_stride_k = strides
+    if scatter is not None:
+        args.row_target, args.peer_out, args.peer_count = scatter.row_target.data_ptr(), scatter.peer_out, scatter.world
     args.status = _native.status_words(device.index).data_ptr()
     current = torch.cuda.current_device() == device.index
     stream = torch.cuda.current_stream(device).cuda_stream
@@ -286,7 +300,7 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
 
 def fp8_nvfp4_grouped_gemm(a: torch.Tensor, a_scale: torch.Tensor, experts: NVFP4Experts, routing: Routing, m: int,
                            out: torch.Tensor | None = None, config: GemmConfig | None = None, enable_pdl: bool = False,
-                           *, group_scales: bool = False) -> torch.Tensor:
+                           *, group_scales: bool = False, scatter: PeerScatter | None = None) -> torch.Tensor:
     """Each expert's `(a_e * a_scale_e) @ dequant(experts.expert(e)).T` in one launch, BF16 out.
 
     `a_scale` is `[rows, 1]`, or `[rows, K/128]` (masked: optionally `[E, capacity, K/128]`) with `group_scales=True`,
@@ -350,6 +364,11 @@ def fp8_nvfp4_grouped_gemm(a: torch.Tensor, a_scale: torch.Tensor, experts: NVFP
         scratch = _gather_buffer(a.device, routing.sorted_ids.numel() * k) if USE_GATHER_PASS else None
         if scratch is not None:
             r.gather_scratch, r.gather_scratch_bytes = scratch.data_ptr(), scratch.numel()
+    if scatter is not None:
+        _require(layout in ("masked", "contiguous"), "scattered output rows go with masked or contiguous routing")
+        t = scatter.row_target
+        _require(t.is_cuda and t.device == a.device and t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= rows,
+                 f"scatter.row_target must be a contiguous int32 tensor of at least {rows} entries on the device of a")
     _launch(a, a_scale, strides, experts.weight, experts.scale, experts.global_scale, experts.locks, d, rows, n, k,
-            experts.bridge, group_scales, enable_pdl, config, r)
+            experts.bridge, group_scales, enable_pdl, config, r, scatter=scatter)
     return d

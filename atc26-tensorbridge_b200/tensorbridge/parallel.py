@@ -278,6 +278,8 @@ class PeerDispatch:
     out: torch.Tensor  # BF16 [E_local * capacity, N]: where the masked GEMM must write (`out=`)
     dest_row: torch.Tensor  # int32 [T * top_k]: row of every route in its owner's buffers (-1 = dropped)
     topk_ids: torch.Tensor
+    scatter: object = None  # `tensorbridge.PeerScatter` for the GEMM when the combine is fused into its epilogue
+    routes: torch.Tensor | None = None  # BF16 [T * top_k, N]: where the fused combine delivers this rank's routes
 
 
 class PeerMaskedExchange:
@@ -291,12 +293,20 @@ class PeerMaskedExchange:
         tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, experts, tb.MaskedRouting(plan.counts), m, out=plan.out)
         y = exchange.combine(plan)                                   # barrier, pull
 
+    or, with the combine fused into the GEMM's epilogue (every output row stored over NVLink into the route buffer of the
+    rank it came from, tile by tile as the GEMM produces it):
+
+        plan = exchange.dispatch(x_q, x_scale, topk_ids, fused_combine=True)
+        tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, experts, tb.MaskedRouting(plan.counts), m, out=plan.out,
+                                  scatter=plan.scatter)
+        y = exchange.finish(plan)                                    # barrier
+
     and launches nothing but this library's kernels: no host read, so it can follow a quantiser and precede the next
     layer without a synchronisation.  The masked buffers are reused by the next `dispatch`: consume `y` (a fresh
     tensor) as you like, but read `plan.a` / `plan.out` only before the next step.  `close()` unmaps and frees."""
 
     def __init__(self, num_experts: int, capacity: int, k: int, groups: int, n: int, group=None,
-                 placement: str = "interleaved", wait_us: int = 0) -> None:
+                 placement: str = "interleaved", wait_us: int = 0, max_routes: int = 0) -> None:
         from tensorbridge import _native  # noqa: PLC0415
         self._native, self._lib = _native, _native.load()
         self.group = group
@@ -312,7 +322,8 @@ class PeerMaskedExchange:
         self.placement, self.wait_us = placement, wait_us
         self.device = torch.device("cuda", torch.cuda.current_device())
         rows = self.e_local * capacity
-        sizes = [rows * k, rows * groups * 4, rows * n * 2, self.world * num_experts * 4, 256]
+        self.max_routes = max_routes
+        sizes = [rows * k, rows * groups * 4, rows * n * 2, self.world * num_experts * 4, 256, rows * 4, max(max_routes, 1) * n * 2]
         self._offsets, total = [], 0
         for size in sizes:
             self._offsets.append(total)
@@ -339,6 +350,9 @@ class PeerMaskedExchange:
 
         self._peer_a, self._peer_scale, self._peer_y = pointers(0), pointers(1), pointers(2)
         self._peer_counts, self._peer_flags = pointers(3), pointers(4)
+        self._peer_targets, self._peer_routes = pointers(5), pointers(6)
+        self.row_target = _alias(self._base + self._offsets[5], (rows,), torch.int32, self.device)
+        self.routes = _alias(self._base + self._offsets[6], (max(max_routes, 1), n), torch.bfloat16, self.device)
         self.a = _alias(self._base + self._offsets[0], (rows, k), torch.float8_e4m3fn, self.device)
         self.a_scale = _alias(self._base + self._offsets[1], (rows, groups), torch.float32, self.device)
         self.out = _alias(self._base + self._offsets[2], (rows, n), torch.bfloat16, self.device)
@@ -355,9 +369,17 @@ class PeerMaskedExchange:
             0 if payload is None else payload.numel(), self.rank, self.world, self._epoch.data_ptr(), self.wait_us,
             native.status_words(self.device.index).data_ptr()))
 
-    def dispatch(self, x_q: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor) -> PeerDispatch:
+    def dispatch(self, x_q: torch.Tensor, x_scale: torch.Tensor, topk_ids: torch.Tensor, *, fused_combine: bool = False
+                 ) -> PeerDispatch:
+        """Plan, exchange the counts, push the rows.  With `fused_combine` (needs `max_routes >= T * top_k` at
+        construction) the push also tells every owner which rank and route each of its rows belongs to, clears this
+        rank's rows of dropped routes, and the returned plan carries the `scatter` to hand to
+        `fp8_nvfp4_grouped_gemm(..., scatter=plan.scatter)`: the GEMM's epilogue then stores every output row into the
+        route buffer of the rank it came from, and `finish(plan)` (one barrier) returns this rank's routes."""
         native = self._native
         t, top_k = topk_ids.shape
+        if fused_combine and t * top_k > self.max_routes:
+            raise ValueError(f"{t * top_k} routes exceed the exchange's max_routes = {self.max_routes}")
         if x_q.size(1) != self.k or x_scale.reshape(t, -1).size(1) != self.groups or not x_q.is_contiguous():
             raise ValueError("activations do not match the exchange's K / scale groups")
         ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) and topk_ids.is_contiguous() else topk_ids.to(torch.int64).contiguous()
@@ -374,10 +396,25 @@ class PeerMaskedExchange:
             args = native.PushArgs(ids.data_ptr(), int(ids.dtype == torch.int64), top_k, routes, x_q.data_ptr(), scale.data_ptr(),
                                    self.k, self.groups, route_rank.data_ptr(), self.all_counts.data_ptr(), self.num_experts,
                                    self.world, self.rank, interleaved, self.capacity, 0, self._peer_a, self._peer_scale,
-                                   dest_row.data_ptr(), self.counts.data_ptr())
+                                   dest_row.data_ptr(), self.counts.data_ptr(),
+                                   self._peer_targets if fused_combine else None,
+                                   self.routes.data_ptr() if fused_combine else None, self.n * 2)
             native.check(self._lib.tb_ep_push(stream, ctypes.byref(args)))
             self._barrier(stream)  # every rank's rows have landed
+        if fused_combine:
+            from tensorbridge.gemm import PeerScatter  # noqa: PLC0415
+            return PeerDispatch(self.a, self.a_scale, self.counts, self.out, dest_row, ids,
+                                PeerScatter(self.row_target, self._peer_routes, self.world), self.routes[:routes])
         return PeerDispatch(self.a, self.a_scale, self.counts, self.out, dest_row, ids)
+
+    def finish(self, plan: PeerDispatch) -> torch.Tensor:
+        """After the GEMM of a `fused_combine` step: waits (one barrier) until every rank's epilogue has delivered, and
+        returns this rank's routes `[T * top_k, N]` -- a view of the exchange's buffer, valid until the next dispatch."""
+        if plan.routes is None:
+            raise ValueError("finish() follows dispatch(fused_combine=True); use combine() otherwise")
+        with torch.cuda.device(self.device):
+            self._barrier(self._native.stream_ptr(self.device))
+        return plan.routes
 
     def combine(self, plan: PeerDispatch) -> torch.Tensor:
         """`[T * top_k, N]` in route order: every route's row of the owner's GEMM output, zeros for dropped routes."""

@@ -522,7 +522,7 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
 
             exchange, why_not = None, None
             try:
-                exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement="interleaved")
+                exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement="interleaved", max_routes=routes)
             except Exception as exc:  # noqa: BLE001  peer mapping unavailable on this box: the collective path is timed alone
                 why_not = f"{type(exc).__name__}: {exc}"
             usable = torch.tensor([exchange is not None], device=dev, dtype=torch.int32)
@@ -540,6 +540,22 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
                 if events:
                     gemm_stop.record()
                 result = exchange.combine(plan)
+                if timed:
+                    gemm_stop.synchronize()
+                    gemm_ms.append(gemm_start.elapsed_time(gemm_stop))
+                return result, plan
+
+            def fused_step(timed: bool = False, events: bool = True):
+                # the combine fused into the GEMM's epilogue: every output row is stored into its origin rank's buffer
+                q, s = fp8.quantize(x)
+                plan = exchange.dispatch(q, s, ids, fused_combine=True)
+                if events:
+                    gemm_start.record()
+                tb.fp8_nvfp4_grouped_gemm(plan.a, plan.a_scale, ex, tb.MaskedRouting(plan.counts), routes, out=plan.out,
+                                          scatter=plan.scatter)
+                if events:
+                    gemm_stop.record()
+                result = exchange.finish(plan)
                 if timed:
                     gemm_stop.synchronize()
                     gemm_ms.append(gemm_start.elapsed_time(gemm_stop))
@@ -574,6 +590,10 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
                 peer_result, _ = peer_step()
                 if not torch.equal(peer_result, result):
                     raise SystemExit(f"peer-memory exchange disagrees with the collective path at T = {local_tokens * world} on rank {rank}")
+                fused_result, _ = fused_step()
+                torch.cuda.synchronize()
+                if not torch.equal(fused_result, result):
+                    raise SystemExit(f"fused combine disagrees with the collective path at T = {local_tokens * world} on rank {rank}")
                 tb.check_status()
 
             def time_steps(step):
@@ -590,18 +610,19 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
                 return max_over_ranks(start.elapsed_time(stop) / reps), max_over_ranks(sum(gemm_ms) / len(gemm_ms))
 
             nccl_ms, nccl_gemm_ms = time_steps(collective_step)
-            step_ms, g_ms = time_steps(peer_step) if exchange is not None else (nccl_ms, nccl_gemm_ms)
+            pull_ms, pull_gemm_ms = time_steps(peer_step) if exchange is not None else (nccl_ms, nccl_gemm_ms)
+            step_ms, g_ms = time_steps(fused_step) if exchange is not None else (nccl_ms, nccl_gemm_ms)
             graph_ms = None
             if exchange is not None:
                 # the whole step reads nothing back to the host, so it replays from one CUDA graph per rank
                 side = torch.cuda.Stream(device=dev)
                 side.wait_stream(torch.cuda.current_stream(dev))
                 with torch.cuda.stream(side):
-                    peer_step(events=False)
+                    fused_step(events=False)
                     side.synchronize()
                     step_graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(step_graph, stream=side):
-                        graph_result, _ = peer_step(events=False)
+                        graph_result, _ = fused_step(events=False)
                     for _ in range(3):
                         step_graph.replay()
                     side.synchronize()
@@ -620,12 +641,13 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
             best_ms = min(step_ms, graph_ms) if graph_ms is not None else step_ms
             routed = sum_over_ranks(kept)
             rows_out.append({"tokens": local_tokens * world, "capacity": capacity,
-                             "exchange": "peer memory (NVLink loads/stores by the library's kernels)" if exchange is not None
+                             "exchange": "peer memory (NVLink stores by the library's kernels; combine fused into the GEMM's epilogue)" if exchange is not None
                                          else f"NCCL all-to-all (peer mapping unavailable: {why_not})",
                              "step_ms": round(step_ms, 4), "gemm_ms": round(g_ms, 4),
                              "dispatch_combine_ms": round(step_ms - g_ms, 4),
                              "step_ms_graph": None if graph_ms is None else round(graph_ms, 4),
-                             "tokens_per_s": round(local_tokens * world / best_ms * 1e3, 1), "step_ms_nccl": round(nccl_ms, 4), "routes_kept": int(routed), "routes": local_tokens * world * top_k,
+                             "tokens_per_s": round(local_tokens * world / best_ms * 1e3, 1),
+                             "step_ms_separate_combine": round(pull_ms, 4), "step_ms_nccl": round(nccl_ms, 4), "routes_kept": int(routed), "routes": local_tokens * world * top_k,
                              "gemm_tflops": round(2.0 * routed * n * k / g_ms / 1e9, 1)})
             if exchange is not None:
                 exchange.close()
@@ -634,7 +656,8 @@ def run_sharded(args, tb, dist, dev, rank: int, world: int) -> dict:
         out["moe_masked_expert_parallel"] = {
             "config": "benchmark config 3: E=256 (E/n_gpus per GPU, interleaved placement), N=4096, K=7168, top_k=8, Zipf(1.1) routing; "
                       "step = fp8.quantize -> dispatch -> masked grouped GEMM -> combine; over peer memory (plan, barrier carrying the "
-                      "counts, push, barrier, GEMM, barrier, pull: no host read) and, as step_ms_nccl, over NCCL (counts all-to-all, host "
+                      "counts, push, barrier, GEMM whose epilogue stores every row into its origin rank's buffer, barrier: no host "
+                      "read; step_ms_separate_combine: GEMM into a local buffer, barrier, pull kernel) and, as step_ms_nccl, over NCCL (counts all-to-all, host "
                       "read of the split sizes, packed-row all-to-all, place, GEMM, gather, all-to-all, gather); strong scaling in tokens, "
                       "weights sharded",
             "experts_per_gpu": e_local, "results": rows_out}

@@ -214,6 +214,13 @@ typedef struct tb_gemm_args {
                              * second.  A wait that runs out makes the kernel return early and write `status`. */
     int32_t only_split;     /* test hook, dense K splits only: s + 1 runs just the units of split s, so that its peers'
                              * partial sums never arrive and its bounded wait runs out; 0 = all units (normal use) */
+    const int32_t* row_target; /* grouped masked / contiguous launches of an expert-parallel step, else NULL: int32 [rows],
+                             * row r of `a` belongs to route (row_target[r] & 0x3FFFFFF) of rank (row_target[r] >> 26), -1 =
+                             * nobody's; the epilogue then stores the row's output straight into that rank's buffer
+                             * peer_out[rank] (row stride n elements; plain stores over NVLink) instead of `d` */
+    void* const* peer_out;  /* host array of peer_count device pointers (every rank's BF16 route buffer, as mapped here) */
+    int32_t peer_count;     /* 1..16 */
+    int32_t reserved;
 } tb_gemm_args;
 
 /* D[m, n] = bf16((A @ bridge(W).T) * a_scale * global_scale).
@@ -300,7 +307,10 @@ int tb_gather_rows(void* stream, const void* src, const int32_t* index, int64_t 
  * mapped: the masked activation buffer a [E/W * capacity, width] and a_scale [E/W * capacity, groups], the output
  * buffer y [E/W * capacity, n], a count matrix int32 [W][E] and W arrival flags (uint32, zero at start).  One step:
  *   tb_ep_plan (route_rank, send_counts) -> tb_peer_barrier carrying send_counts into row `rank` of every peer's count
- *   matrix -> tb_ep_push -> tb_peer_barrier -> tb_gemm_grouped (masked) into y -> tb_peer_barrier -> tb_ep_pull.
+ *   matrix -> tb_ep_push -> tb_peer_barrier -> tb_gemm_grouped (masked) into y -> tb_peer_barrier -> tb_ep_pull;
+ *   or, with the combine fused into the GEMM's epilogue: ... tb_ep_push (also fills the owners' row_target tables) ->
+ *   tb_peer_barrier -> tb_gemm_grouped with row_target / peer_out (every output row is stored into the buffer of the rank
+ *   its route came from) -> tb_peer_barrier.
  * Only plain loads and stores cross NVLink (no TMA on peer memory, no multicast). */
 
 /* Set-up helpers for that memory.  These four are the only entry points of the library that allocate, free or map
@@ -345,6 +355,12 @@ typedef struct tb_ep_push_args {
     void* const* peer_a_scale; /* ... and scale buffer */
     int32_t* dest_row;
     int32_t* counts;
+    void* const* peer_row_target; /* optional: every rank's int32 [E/W * capacity] table; the row a route lands in gets
+                                   * (rank << 26 | route), which tb_gemm_grouped takes as row_target to return the row's
+                                   * output to this rank without a combine pass */
+    void* out;                 /* optional, with peer_row_target: this rank's route buffer [routes, out_row_bytes]; the
+                                * rows of routes that were not sent are cleared here */
+    int64_t out_row_bytes;     /* multiple of 16 */
 } tb_ep_push_args;
 
 int tb_ep_push(void* stream, const tb_ep_push_args* args);

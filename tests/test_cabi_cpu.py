@@ -31,7 +31,7 @@ def test_struct_sizes_match_header(lib):
     from tensorbridge import _native
     assert ctypes.sizeof(_native.Config) == 36
     assert ctypes.sizeof(_native.Problem) == 48
-    assert ctypes.sizeof(_native.GemmArgs) == 18 * 8  # 17 eight-byte slots + wait_us, only_split
+    assert ctypes.sizeof(_native.GemmArgs) == 21 * 8  # + wait_us / only_split, row_target, peer_out, peer_count / reserved
     assert ctypes.sizeof(_native.Routing) == 8 + 5 * 8 + 8 + 8 + 16
 
 

@@ -152,7 +152,8 @@ def test_peer_memory_exchange_matches_the_collective_path(one_rank_group, placem
     from tensorbridge import parallel
     experts, n, k, tokens, top_k, capacity = 4, 128, 256, 24, 2, 8
     views, ex, q, s, ids, wq, ws = _moe_case(experts, n, k, tokens, top_k, [0.55, 0.25, 0.1, 0.1], seed=700)
-    exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement=placement, wait_us=2_000_000)
+    exchange = parallel.PeerMaskedExchange(experts, capacity, k, 1, n, placement=placement, wait_us=2_000_000,
+                                           max_routes=tokens * top_k)
     try:
         for step in range(2):
             step_ids = ids if step == 0 else ids.flip(0).contiguous()
@@ -172,6 +173,13 @@ def test_peer_memory_exchange_matches_the_collective_path(one_rank_group, placem
             want_back = parallel.combine_masked(want_y, want_plan, tokens * top_k)
             tb.check_status()
             assert torch.equal(back, want_back)
+            # the combine fused into the GEMM's epilogue delivers the same rows
+            fused = exchange.dispatch(q, s, step_ids, fused_combine=True)
+            tb.fp8_nvfp4_grouped_gemm(fused.a, fused.a_scale, weights, tb.MaskedRouting(fused.counts), tokens * top_k,
+                                      out=fused.out, scatter=fused.scatter)
+            delivered = exchange.finish(fused)
+            tb.check_status()
+            assert torch.equal(delivered, want_back)
             del order
         if placement == "contiguous":
             assert _check_routes(back, ids.flip(0), views, wq, ws, capacity, n, k, top_k) > 0
