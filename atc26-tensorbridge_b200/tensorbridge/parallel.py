@@ -303,10 +303,12 @@ class PeerMaskedExchange:
 
     and launches nothing but this library's kernels: no host read, so it can follow a quantiser and precede the next
     layer without a synchronisation.  The masked buffers are reused by the next `dispatch`: consume `y` (a fresh
-    tensor) as you like, but read `plan.a` / `plan.out` only before the next step.  `close()` unmaps and frees."""
+    tensor) as you like, but read `plan.a` / `plan.out` only before the next step.  `wait_us` bounds every barrier wait
+    (ten seconds by default: ranks reach their first barrier at different times, after loading kernels); a barrier that
+    runs out writes `100 + peer` to the status words (`tensorbridge.check_status()` raises).  `close()` unmaps and frees."""
 
     def __init__(self, num_experts: int, capacity: int, k: int, groups: int, n: int, group=None,
-                 placement: str = "interleaved", wait_us: int = 0, max_routes: int = 0) -> None:
+                 placement: str = "interleaved", wait_us: int = 10_000_000, max_routes: int = 0) -> None:
         from tensorbridge import _native  # noqa: PLC0415
         self._native, self._lib = _native, _native.load()
         self.group = group
@@ -336,14 +338,29 @@ class PeerMaskedExchange:
         handles = [None] * self.world
         dist.all_gather_object(handles, (os.getpid(), handle.raw), group=group)
         self._peer_bases, self._opened = [], []
+        failure = None
         for r, (pid, raw) in enumerate(handles):
             if r == self.rank or pid == os.getpid():
                 self._peer_bases.append(self._base)
                 continue
             mapped = ctypes.c_void_p()
-            _native.check(self._lib.tb_ipc_open(raw, ctypes.byref(mapped)))
+            code = self._lib.tb_ipc_open(raw, ctypes.byref(mapped))
+            if code:
+                failure = f"mapping the slab of rank {r}: {self._lib.tb_last_error().decode()}"
+                break
             self._peer_bases.append(mapped.value)
             self._opened.append(mapped.value)
+        # every rank learns whether every rank could map every slab: either all go on or all give up together, so that
+        # no rank is left waiting in a collective for one that raised
+        agreed = torch.tensor([0 if failure is None else 1], dtype=torch.int32, device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX, group=group)
+        if int(agreed.item()):
+            for pointer in self._opened:
+                self._lib.tb_ipc_close(pointer)
+            dist.barrier(group=group)
+            self._lib.tb_peer_free(self._base)
+            self._base, self._opened = None, []
+            raise RuntimeError(failure or "a peer could not map the slabs of the exchange")
 
         def pointers(index: int):
             return (ctypes.c_void_p * self.world)(*[b + self._offsets[index] for b in self._peer_bases])

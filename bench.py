@@ -36,6 +36,7 @@ FP32 torch matmul on the host cores, the code in oracle/) over the same M list, 
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -148,7 +149,8 @@ def init_distributed(local: int):
         os.environ["MASTER_PORT"] = str(29600 + os.getpid() % 300)
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # a rank that fails must not leave the others waiting in a collective for the default ten minutes
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     return dist
 
 

@@ -404,3 +404,43 @@ def test_moe_forward_custom_activation():
     valid = torch.from_numpy(np.concatenate([np.arange(capacity) < c for c in counts]))
     a, b = fused["output"].float().cpu()[valid], custom["output"].float().cpu()[valid]
     assert float((a - b).norm() / a.norm()) <= 5e-3
+
+
+def test_vllm_style_linear_method_without_vllm():
+    """`TensorBridgeLinearMethod` on a plain module: the loader's parameters are swapped for the kernel layout, a fused
+    layer of two shards with different global scales is brought to a shared one, bias is added, leading dimensions kept."""
+    import tensorbridge as tb
+    from tensorbridge import vllm_plugin
+    from tensorbridge.quant import nvfp4
+    shards, k = [128, 256], 512
+    layer = torch.nn.Module()
+    method = vllm_plugin.TensorBridgeLinearMethod(bridge="exact")
+    method.create_weights(layer, k, shards, k, sum(shards), torch.bfloat16)
+    weights = [seeded_weight(n, k, seed=40 + i, std=0.02 * (i + 1)) for i, n in enumerate(shards)]
+    packed, scales, multipliers = zip(*(nvfp4.quantize(w) for w in weights))
+    layer.weight.data = torch.cat(packed).cuda()
+    layer.weight_scale.data = torch.cat(scales).cuda()
+    layer.weight_scale_2.data = torch.cat(multipliers).cuda()
+    assert vllm_plugin.unsupported_linear_reason(layer) is None
+    method.process_weights_after_loading(layer)
+    assert not hasattr(layer, "weight") and layer.tensorbridge_weight.dtype == torch.int32
+    x = seeded_activations(6, k, seed=50).cuda().view(2, 3, k)
+    bias = torch.full((sum(shards),), 0.5, dtype=torch.bfloat16, device="cuda")
+    out = method.apply(layer, x, bias)
+    tb.check_status()
+    assert out.shape == (2, 3, sum(shards))
+    # reference: each shard's own dequantised weight (the shared global scale only re-rounds the smaller shard's group
+    # scales to E4M3, a relative step of at most 2^-4 on single groups)
+    ref = torch.cat([orc_dequant(w).cuda() for w in weights]).float()
+    want = x.float().view(6, k) @ ref.T + 0.5
+    err = float((out.float().view(6, -1) - want).norm() / want.norm())
+    assert err < 0.2, err  # a sanity bound: FP8 activations and 4-bit weights against the unquantised product (about 0.1)
+    with pytest.raises(ValueError):
+        method.apply(layer, x.float(), None)
+    with pytest.raises(ValueError):
+        vllm_plugin.TensorBridgeLinearMethod().create_weights(torch.nn.Module(), 24, [8], 24, 8, torch.bfloat16)
+
+
+def orc_dequant(w):
+    """The BF16 weight itself (what quantisation approximates)."""
+    return w.float()
