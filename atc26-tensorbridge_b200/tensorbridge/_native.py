@@ -174,7 +174,13 @@ def check(code: int) -> None:
     raise RuntimeError(message)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device: torch.device | int) -> int:
+    """The `cudaStream_t` of torch's current stream on `device`, as an integer."""
+    if _raw_stream is not None:
+        return _raw_stream(device if isinstance(device, int) else device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 

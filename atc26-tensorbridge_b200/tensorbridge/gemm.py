@@ -173,15 +173,16 @@ class _Call:
 
 _dense_calls: dict[tuple, _Call] = {}
 # Argument structs of dense calls whose every pointer is fixed (see `fp8_nvfp4_gemm`).
-_repeat_calls: dict[tuple, _Call] = {}
+_repeat_calls: dict[tuple, tuple] = {}
 
 
 def _relaunch(call: _Call, device: torch.device) -> None:
     """Launch `call` again as it stands: only the stream, its split-K scratch and the status words are looked up."""
     lib = _native.load()
     args = call.args
-    args.status = _native.status_words(device.index).data_ptr()
-    stream = torch.cuda.current_stream(device).cuda_stream
+    index = device.index
+    args.status = _native.status_words(index).data_ptr()
+    stream = _native.stream_ptr(index)
     cfg_ref = call.cfg_ref
     if call.need > 0:
         workspace = _workspace(device, call.need, stream)
@@ -190,7 +191,7 @@ def _relaunch(call: _Call, device: torch.device) -> None:
             args.workspace, args.workspace_bytes = None, 0
         else:
             args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
-    if torch.cuda.current_device() == device.index:
+    if torch.cuda.current_device() == index:
         code = lib.tb_gemm_dense(stream, call.args_ref, cfg_ref)
     else:
         with torch.cuda.device(device):
@@ -221,7 +222,7 @@ def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, ro
         args.row_target, args.peer_out, args.peer_count = scatter.row_target.data_ptr(), scatter.peer_out, scatter.world
     args.status = _native.status_words(device.index).data_ptr()
     current = torch.cuda.current_device() == device.index
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _native.stream_ptr(device.index)
     cfg_ref = call.cfg_ref
     if call.need > 0:
         workspace = _workspace(device, call.need, stream)
@@ -258,14 +259,16 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
     """
     n, k = weight.shape
     repeat_key = None
+    config_in = config
     if out is not None:
         # A call that repeats an earlier one pointer for pointer (a serving loop over static buffers) skips the checks
         # it has passed before and relaunches with the argument structs of that call.
         repeat_key = (weight.weight.data_ptr(), weight.scale.data_ptr(), n, k, weight.bridge, a.data_ptr(), a_scale.data_ptr(),
-                      out.data_ptr(), a.size(0), a.dtype, out.dtype, int(enable_pdl), config, group_scales)
+                      out.data_ptr(), a.size(0), a.dtype, out.dtype, int(enable_pdl), id(config), group_scales)
         again = _repeat_calls.get(repeat_key)
-        if again is not None and a.is_contiguous() and out.is_contiguous() and a_scale.size(0) == a.size(0):
-            _relaunch(again, a.device)
+        if (again is not None and again[1] is config and a.is_contiguous() and out.is_contiguous()
+                and a_scale.size(0) == a.size(0)):
+            _relaunch(again[0], a.device)
             return out
     strides = _check_common(a, a_scale, k, group_scales)
     m = a.size(0)
@@ -293,8 +296,9 @@ def fp8_nvfp4_gemm(a: torch.Tensor, a_scale: torch.Tensor, weight: NVFP4Weight, 
     if repeat_key is not None:
         if len(_repeat_calls) > 4096:
             _repeat_calls.clear()
-        _repeat_calls[repeat_key] = _Call(_native.GemmArgs.from_buffer_copy(call.args), _native.Config.from_buffer_copy(call.cfg),
-                                          None, call.need)
+        # (keyed by the identity of `config`: the entry keeps the object alive, so the id cannot be reused while it is here)
+        _repeat_calls[repeat_key] = (_Call(_native.GemmArgs.from_buffer_copy(call.args), _native.Config.from_buffer_copy(call.cfg),
+                                           None, call.need), config_in)
     return d
 
 
