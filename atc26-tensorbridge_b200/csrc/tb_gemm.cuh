@@ -636,6 +636,15 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         sc[i][1] = scales[(c0 + 1) * 128 + r];
                     }
                 }
+                // Convert first, into registers: the stage of the bridged ring may still be feeding the tensor core, and
+                // only the stores have to wait for it.
+                uint4 fp8[kVecsPerThread][2];
+#pragma unroll
+                for (int i = 0; i < kVecsPerThread; ++i) {
+                    const BridgeTables<kExact> t0(sc[i][0]), t1(sc[i][1]);
+                    fp8[i][0] = t0.chunk(v[i].x, v[i].y);
+                    fp8[i][1] = t1.chunk(v[i].z, v[i].w);
+                }
                 [[maybe_unused]] const uint32_t w1 = TB_CLOCK();
                 if (!__all_sync(0xffffffffu, mbar_wait(br_empty(bs), bphase ^ 1u, abort_flag, kWaitBridgedEmpty, 0, p.wait_cycles))) { ok = false; break; }
                 waited_empty += TB_CLOCK() - w1;
@@ -643,9 +652,8 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
 #pragma unroll
                 for (int i = 0; i < kVecsPerThread; ++i) {
                     const int vec = bt + i * kTeamThreads;
-                    const BridgeTables<kExact> t0(sc[i][0]), t1(sc[i][1]);
                     // 32 K values of this row: columns 8 * (vec / 128) .. +7 of the stage
-                    tmem_st_8(a_lane + bs * kTileCols + (vec >> 7) * 8, t0.chunk(v[i].x, v[i].y), t1.chunk(v[i].z, v[i].w));
+                    tmem_st_8(a_lane + bs * kTileCols + (vec >> 7) * 8, fp8[i][0], fp8[i][1]);
                 }
                 tmem_st_wait();
                 tc_fence_before_sync();
