@@ -267,12 +267,16 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             prefetch_tensormap(&p.map_a);
             prefetch_tensormap(&p.map_sf);
         }
-        // All barrier slots, used or not, one per lane and pass: arrival counts by slot range.
+        // The weight ring's barriers (full, then empty), one per lane: all this warp needs before its first copy.
+        static_assert(2 * kMaxRawStages <= 32, "one lane per barrier of the weight ring");
+        if (lane < 2 * kMaxRawStages) mbar_init(bar0 + 8u * lane, lane < kMaxRawStages ? 1u : kArrivals);
+        fence_barrier_init();
+    } else if (warp == kActWarp) {
+        // Every other barrier slot, used or not, one per lane and pass: arrival counts by slot range.
         constexpr int kSlots = 4 * kMaxRawStages + 2 * kMaxBridgedStages + 2 * kMaxAccSets + 1;
-        for (int slot = lane; slot < kSlots; slot += 32) {
-            uint32_t count = 1u;  // w_full, a_empty, br_empty, acc_full, drain: one arrival (expect_tx or a commit)
-            if (slot >= kMaxRawStages && slot < 2 * kMaxRawStages) count = kArrivals;                          // w_empty
-            else if (slot >= 2 * kMaxRawStages && slot < 3 * kMaxRawStages) count = gather ? 32u : 1u;          // a_full
+        for (int slot = 2 * kMaxRawStages + lane; slot < kSlots; slot += 32) {
+            uint32_t count = 1u;  // a_empty, br_empty, acc_full, drain: one arrival (expect_tx or a commit)
+            if (slot < 3 * kMaxRawStages) count = gather ? 32u : 1u;                                             // a_full
             else if (slot >= 4 * kMaxRawStages && slot < 4 * kMaxRawStages + kMaxBridgedStages) count = kArrivals;  // br_full
             else if (slot >= 4 * kMaxRawStages + 2 * kMaxBridgedStages + kMaxAccSets && slot < kSlots - 1) count = kEpilogueWarps;  // acc_empty
             mbar_init(bar0 + 8u * slot, count);
