@@ -47,6 +47,11 @@ constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K wo
 constexpr int kMaxOutputPeers = 16;   // ranks whose buffers an epilogue can scatter to
 constexpr int kMaxSplitTiles = 128;  // output tiles of a K-split launch: the tile index takes 7 bits of a tag
 constexpr int kTransposeBytes = 16 * 32 * 2;  // an epilogue warp's 16-column chunk as BF16 [token][channel]
+// Chunks of turned output an epilogue warp can park in shared memory.  The 256-token tile has one accumulator set, so
+// its drain stands between two main loops: the warps move the accumulator out as fast as tensor memory gives it up --
+// six of a warp's eight chunks into shared memory, two into registers as packed BF16 -- hand the accumulator back, and
+// write the output while the next tile's main loop runs.  Smaller tiles have a second accumulator set instead.
+__host__ __device__ constexpr int staged_chunks(int bm) { return bm == 256 ? 6 : 1; }
 constexpr int kBarrierBytes = 832;     // 4 * 16 + 2 * 8 + 2 * 8 + 1 barriers of 8 bytes, padded
 
 // Epilogue warps of a token tile: four cover the 128 tensor-memory lanes; from 64 tokens up a second set of four takes
@@ -155,14 +160,21 @@ __host__ __device__ constexpr int max_bridged_stages(int bm, bool group_scales) 
 // two bridge warpgroups give registers back (setmaxnreg.dec) and the two epilogue warpgroups take them
 // (setmaxnreg.inc).  inc waits until the pool holds enough, so the sum of the two targets must not exceed twice the
 // kernel's own count: the host checks that count before it launches such an instance.
-constexpr int kRebalancedBridgeRegs = 64;
-constexpr int kRebalancedEpilogueRegs = 128;
 __host__ __device__ constexpr bool rebalances_registers(int bm, bool group_scales, int bridge_warps) {
-    return group_scales && bm == 128 && bridge_warps == 8;
+    return (group_scales && bm == 128 && bridge_warps == 8) || (!group_scales && bm == 256 && bridge_warps == 16);
 }
+// The same on the 256-token tile with per-token scales: its epilogue warps hold part of the converted output in
+// registers while they hand the accumulator back; sixteen bridge warps give eight registers each.
+__host__ __device__ constexpr int rebalanced_bridge_regs(int bm) { return 64 + 0 * bm; }
+__host__ __device__ constexpr int rebalanced_epilogue_regs(int bm) { return bm == 256 ? 88 : 128; }
+// Registers per thread the kernel must have been built with for the pool to cover the epilogue's share.
 __host__ __device__ constexpr int min_kernel_registers(int bm, bool group_scales, int bridge_warps) {
-    return rebalances_registers(bm, group_scales, bridge_warps) ? (kRebalancedBridgeRegs + kRebalancedEpilogueRegs) / 2 : 0;
+    return !rebalances_registers(bm, group_scales, bridge_warps) ? 0
+           : (bridge_warps * rebalanced_bridge_regs(bm) + epilogue_warps(bm) * rebalanced_epilogue_regs(bm) +
+              bridge_warps + epilogue_warps(bm) - 1) / (bridge_warps + epilogue_warps(bm));
 }
+
+template <int kValue> struct IntC { static constexpr int value = kValue; };
 
 struct SmemLayout {
     uint32_t tokens, token_stage, weights, weight_stage, barriers, misc, ids, epi, transpose, prefix, total;
@@ -179,7 +191,7 @@ __host__ __device__ inline SmemLayout smem_layout(int bm, int w_stages, int a_st
     l.ids = l.misc + 64;
     l.epi = l.ids + 256 * 4;  // per epilogue warp: BM scales + BM output rows
     l.transpose = l.epi + 4 * bm * 8;  // per lane quadrant: bm scales + bm rows, split between its column groups
-    l.prefix = l.transpose + epilogue_warps(bm) * kTransposeBytes;  // per epilogue warp: 16 tokens x 32 channels of BF16
+    l.prefix = l.transpose + epilogue_warps(bm) * staged_chunks(bm) * kTransposeBytes;  // per warp: chunks of 16 tokens x 32 channels of BF16
     l.total = l.prefix + (num_experts > 0 ? (3 * num_experts + 4) * 4 : 0);
     return l;
 }
@@ -597,7 +609,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         }
     } else if (warp >= kEpilogueWarps) {
         // =========================== bridge ===========================
-        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_dec<kRebalancedBridgeRegs>();
+        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_dec<rebalanced_bridge_regs(BM)>();
         // Thread bt of a team owns vectors bt, bt + kTeamThreads, ... of its 128 x 128 block (layout in tb_bridge.cuh).
         const int team = (warp - kEpilogueWarps) / kGroupWarps;
         const int first = team;  // its first K block; then every kTurns-th
@@ -675,7 +687,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         if (warp == kEpilogueWarps && lane == 0) { TB_REPORT(4, TB_CLOCK() - loop_begin); TB_REPORT(5, waited_raw); TB_REPORT(6, waited_empty); }
     } else {
         // =========================== epilogue ===========================
-        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_inc<kRebalancedEpilogueRegs>();
+        if constexpr (rebalances_registers(BM, kGroupScales, kBridgeWarps)) setmaxnreg_inc<rebalanced_epilogue_regs(BM)>();
         const int quad = warp & 3, cgroup = warp >> 2;
         const int col0 = cgroup * kCols;          // first token column of this warp
         const int n_local = quad * 32 + lane;     // TMEM lane = channel within a 128-channel tile
@@ -688,7 +700,9 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         // lanes per row) instead of sixteen 2-byte stores, which the store path takes at a fraction of the rate.
         // (Worked out where they are used: nothing of this stays in registers across the main loop.)
         auto wide = [&]() { return (p.n & 7) == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0; };
-        auto turned_chunk = [&]() { return reinterpret_cast<__nv_bfloat16*>(smem + L.transpose + warp * kTransposeBytes); };
+        auto turned_chunk = [&]() {
+            return reinterpret_cast<__nv_bfloat16*>(smem + L.transpose + warp * (staged_chunks(BM) * kTransposeBytes));
+        };
         // K-split launches number themselves on the device.  Word 0 of the workspace is the sequence of the last launch
         // that ran on it, word 1 counts the CTAs of this launch that have read it; the CTA that arrives last advances the
         // sequence.  By then every CTA of the grid holds its copy, and the next launch on the workspace starts after this
@@ -865,6 +879,96 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 const int n = t.nt * 128 + n_local;
                 const bool n_ok = n < p.n;
                 const bool wide_stores = wide();
+                if constexpr (kAccSets == 1) if (!partial && wide_stores) {
+                    // One accumulator set: everything out of tensor memory first, then the accumulator goes back to the
+                    // MMA warp, then the output is written (while the next tile accumulates).
+                    // A 16-token chunk comes out of tensor memory as two 16-lane loads in the layout of an MMA
+                    // accumulator fragment (lane: channels lane / 4 and + 8, tokens 2 * (lane % 4) and + 1 of each
+                    // 8-token half), is scaled, packed to BF16 pairs and turned around by stmatrix.trans: shared
+                    // memory gets [token][32 channels], 64 bytes a token, the 16-byte words of a row swapped around by
+                    // the token index so that neither the matrix stores nor the row reads collide on banks.
+                    constexpr int kChunks = kCols / 16, kStaged = staged_chunks(BM) < kChunks ? staged_chunks(BM) : kChunks;
+                    constexpr int kKept = kChunks - kStaged;
+                    const uint32_t stage_u32 = smem_u32(turned_chunk());
+                    // stmatrix: lane -> 8-channel group lane / 8, token lane % 8 of a half; the word's slot in its row
+                    const uint32_t st_addr = stage_u32 + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
+                    uint32_t kept[kKept > 0 ? kKept * 8 : 1];
+                    const uint32_t acc_addr = lane_base + acc * BM + col0;
+                    const float* const scale_pair = my_scale + 2 * (lane & 3);
+                    auto step = [&](auto chunk) {
+                        constexpr int c = decltype(chunk)::value;
+                        if (c * 16 < cols_valid) {  // warp-uniform
+                            uint32_t lo[8], hi[8];  // channels 0-15 and 16-31 of the warp's 32
+                            tmem_ld_16x256b_x2(acc_addr + c * 16, lo);
+                            tmem_ld_16x256b_x2(acc_addr + c * 16 + (16u << 16), hi);
+                            tmem_ld_wait_for(lo, hi);
+                            const float2 s0 = *reinterpret_cast<const float2*>(scale_pair + c * 16);
+                            const float2 s1 = *reinterpret_cast<const float2*>(scale_pair + c * 16 + 8);
+                            auto pack = [](uint32_t x, uint32_t y, const float2& sc) {
+                                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(x) * sc.x, __uint_as_float(y) * sc.y);
+                                return *reinterpret_cast<const uint32_t*>(&pair);
+                            };
+                            // words of the first token half (channel groups 0-3), then of the second
+                            const uint32_t w[8] = {pack(lo[0], lo[1], s0), pack(lo[2], lo[3], s0), pack(hi[0], hi[1], s0), pack(hi[2], hi[3], s0),
+                                                   pack(lo[4], lo[5], s1), pack(lo[6], lo[7], s1), pack(hi[4], hi[5], s1), pack(hi[6], hi[7], s1)};
+                            if constexpr (c < kStaged) {
+                                stmatrix_x4_trans(st_addr + c * 1024, w[0], w[1], w[2], w[3]);
+                                stmatrix_x4_trans(st_addr + c * 1024 + 512, w[4], w[5], w[6], w[7]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) kept[(c - kStaged) * 8 + i] = w[i];
+                            }
+                        }
+                    };
+                    static_assert(kChunks == 8, "the drain is written out for eight chunks");
+                    step(IntC<0>{}); step(IntC<1>{}); step(IntC<2>{}); step(IntC<3>{});
+                    step(IntC<4>{}); step(IntC<5>{}); step(IntC<6>{}); step(IntC<7>{});
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty(acc));
+                    // The output: lane -> token lane / 4 (and + 8) of a chunk, 8-channel word lane % 4 of its row.
+                    const int tok = lane >> 2, part = lane & 3;
+                    const int nv = t.nt * 128 + quad * 32 + part * 8;
+                    const bool nv_ok = nv < p.n;
+                    const uint32_t ld_addr = stage_u32 + tok * 64 + ((part ^ ((tok >> 1) & 3)) << 4);
+                    auto write_chunk = [&](int c, int slot) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int col = c * 16 + h * 8 + tok;
+                            const uint4 word = lds_128(ld_addr + slot * 1024 + h * 512);
+                            if (!nv_ok || col >= cols_valid) continue;
+                            if (routed) {
+                                const int row = my_row[col];
+                                if (row >= 0) *reinterpret_cast<uint4*>(out_row_ptr(row) + nv) = word;
+                            } else {
+                                *reinterpret_cast<uint4*>(p.d + static_cast<long long>(t.row0 + col0 + col) * p.n + nv) = word;
+                            }
+                        }
+                    };
+#pragma unroll
+                    for (int c = 0; c < kStaged; ++c) {
+                        if (c * 16 < cols_valid) write_chunk(c, c);
+                    }
+                    if constexpr (kKept > 0) {
+                        __syncwarp();  // the parked chunks have been read: their room takes the chunks kept in registers
+#pragma unroll
+                        for (int c = kStaged; c < kChunks; ++c) {
+                            if (c * 16 < cols_valid) {
+                                const uint32_t* const w = &kept[(c - kStaged) * 8];
+                                stmatrix_x4_trans(st_addr + (c - kStaged) * 1024, w[0], w[1], w[2], w[3]);
+                                stmatrix_x4_trans(st_addr + (c - kStaged) * 1024 + 512, w[4], w[5], w[6], w[7]);
+                            }
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int c = kStaged; c < kChunks; ++c) {
+                            if (c * 16 < cols_valid) write_chunk(c, c - kStaged);
+                        }
+                    }
+                    __syncwarp();  // before the next tile parks its chunks
+                    if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
+                    continue;
+                }
                 if (!partial && !routed && wide_stores) {
                     // Rows of the tile are consecutive rows of the output: one pointer, a fixed step per column.
                     __nv_bfloat16* const turned = turned_chunk();

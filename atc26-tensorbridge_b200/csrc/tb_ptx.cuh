@@ -216,6 +216,35 @@ __device__ __forceinline__ void tmem_st_8(uint32_t taddr, const uint4& a, const 
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 lanes x 16 columns in the layout of an MMA accumulator fragment: thread t gets lanes t / 4 (r0, r1 and r4, r5)
+// and t / 4 + 8 (r2, r3 and r6, r7) of the 16 lanes that start at the address's lane, columns 2 * (t % 4) and + 1 of
+// the first eight columns (r0..r3) and of the second eight (r4..r7).
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+// Waits for the loads in flight, tied to the registers of two of them: nothing that reads those moves above the wait.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&a)[8], uint32_t (&b)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                   "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7])
+                 :
+                 : "memory");
+}
+// Four 8 x 8 matrices of 16-bit elements, transposed on the way: thread t holds elements [t / 4][2 * (t % 4)] and
+// [t / 4][2 * (t % 4) + 1] of each matrix (one register per matrix, first element in the low half); element [r][c]
+// lands at position r of the 16-byte row whose address thread 8 * matrix + c passed.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 lds_128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
 
 // ---- register shares ----------------------------------------------------------------------------------
 // Whole-warpgroup calls (four consecutive warps starting at a multiple of four, all of their threads).
