@@ -218,6 +218,10 @@ int rule(const tb_problem& pr, tb_config* cfg) {
         }
         splits = std::max(1, std::min({splits, k_blocks / 2 > 0 ? k_blocks / 2 : 1, 16}));
         if (tiles > 128 || pr.group_scales) splits = 1;
+        // Sharing the tiles of the last, partial round out in K blocks (use_stream_k = 1) is never picked: the CTA that
+        // finishes a shared tile reads its partners' partial sums one L2 round trip after the other, which costs more
+        // than the idle SMs of the last round (measured at N = 6144, K = 7168: 300 against 294 us at M = 8192, 162
+        // against 153 at 4096, 83 against 79 at 2048).  The path stays for callers that ask for it.
     } else {
         // Routed rows are uneven across experts: a tile of twice the mean rows (at least 32) keeps the busy experts to
         // one or two token tiles, so their weights stream from HBM once; the extra columns cost next to nothing while
@@ -249,6 +253,11 @@ int rule(const tb_problem& pr, tb_config* cfg) {
 }
 
 // Bytes of K-split scratch: the header words, then one 8-byte {partial sum, tag} word per element of every split.
+// Workspace of a balanced launch of `ctas` CTAs: the header, then one partial tile per CTA.
+long long balanced_scratch_bytes(int ctas) {
+    return tb::kEpochCells * 4 + static_cast<long long>(ctas) * tb::kBalancedTileWords * 4;
+}
+
 long long split_scratch_bytes(long long m, long long n, int block_m, int splits) {
     const long long tiles = static_cast<long long>(ceil_div(m, block_m)) * (pad128(n) / 128);
     return tb::kEpochCells * 4 + tiles * splits * block_m * 128 * 8;
@@ -502,6 +511,19 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
 
     p.div_splits = tb::FastDiv::make(static_cast<uint32_t>(p.splits));
     const int grid = static_cast<int>(std::min<long long>(units, sms));
+    // use_stream_k = 1: the tiles of the last, partial round are shared out in even shares of K blocks.  It applies
+    // where it can pay and the kernel has the path: 256-token tiles with per-token scales, more tiles than CTAs and not
+    // a whole number of rounds, at least two K blocks of the shared tiles per CTA, 16-byte output words, a workspace for
+    // the partial sums.  Otherwise the launch runs whole tiles.
+    if (layout == TB_LAYOUT_DENSE && cfg->use_stream_k == 1 && bm == 256 && !a->group_scales && a->only_split == 0) {
+        const long long tiles = units, left = tiles % grid;
+        if (tiles > grid && left > 0 && left * p.k_blocks >= 2ll * grid && grid <= tb::kMaxBalancedCtas &&
+            tiles < (1ll << 24) && a->n % 8 == 0 && reinterpret_cast<uintptr_t>(a->d) % 16 == 0 && a->workspace != nullptr &&
+            reinterpret_cast<uintptr_t>(a->workspace) % 16 == 0 && a->workspace_bytes >= balanced_scratch_bytes(grid)) {
+            p.whole_rounds = static_cast<int>(tiles / grid);
+            p.shared_tiles = static_cast<int>(left);
+        }
+    }
     const bool exact = a->bridge == TB_BRIDGE_EXACT;
     if (a->bridge != TB_BRIDGE_EXACT && a->bridge != TB_BRIDGE_FPMA) return fail(TB_ERR_INVALID, "unknown bridge %d", a->bridge);
     const bool pdl = a->enable_pdl != 0 || p.a_gathered != 0;  // behind its own gather pass the GEMM always chains
@@ -602,7 +624,11 @@ int tb_select_config(const tb_problem* problem, tb_config* config) {
 }
 
 int64_t tb_workspace_bytes(int64_t m, int64_t n, const tb_config* config) {
-    if (config == nullptr || config->use_stream_k <= 1 || m <= 0 || n <= 0 || !(valid_block_m(config->block_m) || jit_block_m(config->block_m))) return 0;
+    if (config == nullptr || config->use_stream_k < 1 || m <= 0 || n <= 0 || !(valid_block_m(config->block_m) || jit_block_m(config->block_m))) return 0;
+    if (config->use_stream_k == 1) {  // balanced shares: a partial tile per CTA, whatever the device (at most 256 SMs)
+        const long long tiles = static_cast<long long>(ceil_div(m, config->block_m)) * (pad128(n) / 128);
+        return config->block_m == 256 && tiles > 1 ? balanced_scratch_bytes(static_cast<int>(std::min<long long>(tiles, 256))) : 0;
+    }
     return split_scratch_bytes(m, n, config->block_m, config->use_stream_k);
 }
 

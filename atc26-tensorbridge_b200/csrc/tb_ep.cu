@@ -105,6 +105,21 @@ int tb_gather_rows(void* stream, const void* src, const int32_t* index, int64_t 
     return TB_OK;
 }
 
+int tb_moe_combine(void* stream, const void* rows, const int32_t* index, const float* weights, int64_t tokens, int32_t top_k,
+                   int64_t width, void* out) {
+    if (tokens < 0 || top_k <= 0 || width <= 0 || width % 8 != 0)
+        return tb::set_last_error(TB_ERR_INVALID, "combine needs top_k > 0 and a width that is a positive multiple of 8");
+    if (tokens == 0) return TB_OK;
+    if (rows == nullptr || weights == nullptr || out == nullptr) return tb::set_last_error(TB_ERR_INVALID, "null tensor pointer");
+    if (reinterpret_cast<uintptr_t>(rows) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0)
+        return tb::set_last_error(TB_ERR_INVALID, "rows and out must be 16-byte aligned");
+    tb::moe_combine_kernel<<<row_grid(tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(rows), index, weights, tokens, top_k, static_cast<int>(width),
+        static_cast<__nv_bfloat16*>(out));
+    TB_EP_CUDA(cudaGetLastError());
+    return TB_OK;
+}
+
 // ---- peer memory ----------------------------------------------------------------------------------------------------
 int tb_peer_alloc(int64_t bytes, void** ptr) {
     if (bytes <= 0 || ptr == nullptr) return tb::set_last_error(TB_ERR_INVALID, "bad allocation request");

@@ -12,6 +12,7 @@
 // The reference has no counterpart: it is handed expert-parallel shapes already dispatched by the serving framework.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -230,6 +231,41 @@ gather_rows16_kernel(const uint8_t* __restrict__ src, const int* __restrict__ in
         } else {
             const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long long>(from) * row_bytes);
             for (int v = lane; v < row_bytes / 16; v += 32) out[v] = in[v];
+        }
+    }
+}
+
+// out[t, :] = bf16(sum over j < top_k of weights[t, j] * rows[r(t, j), :]), r = index[t * top_k + j] (or t * top_k + j
+// without an index); routes whose index is negative add nothing.  The sum runs in FP32 in slot order j = 0, 1, ...,
+// so it is the same from run to run.  One warp per token, eight channels (16 bytes) per lane and step.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ index, const float* __restrict__ weights,
+                   long long tokens, int top_k, int width, __nv_bfloat16* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    for (long long t = warp0; t < tokens; t += warps) {
+        for (int v = lane; v < width / 8; v += 32) {
+            float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < top_k; ++j) {
+                const long long route = t * top_k + j;
+                const long long from = index != nullptr ? index[route] : route;
+                if (from < 0) continue;
+                const float w = weights[route];
+                const uint4 word = *reinterpret_cast<const uint4*>(rows + from * width + v * 8);
+                const __nv_bfloat162* pair = reinterpret_cast<const __nv_bfloat162*>(&word);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(pair[i]);
+                    sum[2 * i] = fmaf(w, f.x, sum[2 * i]);
+                    sum[2 * i + 1] = fmaf(w, f.y, sum[2 * i + 1]);
+                }
+            }
+            uint4 word;
+            __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&word);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pair[i] = __floats2bfloat162_rn(sum[2 * i], sum[2 * i + 1]);
+            *reinterpret_cast<uint4*>(out + t * width + v * 8) = word;
         }
     }
 }

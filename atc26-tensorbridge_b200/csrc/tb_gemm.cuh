@@ -44,6 +44,9 @@ constexpr int kTileCols = 32;  // tensor-memory columns of one bridged FP8 tile:
 constexpr int kTmemCols = 512;
 constexpr int kMaxAccSets = 8;
 constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K workspace: [0] launch sequence, [1] CTAs arrived
+constexpr int kBalancedFlag0 = 16;  // balanced launches: word kBalancedFlag0 + c is raised when CTA c has published its partial tile
+constexpr int kMaxBalancedCtas = kEpochCells - kBalancedFlag0;
+constexpr int kBalancedTileWords = 128 * 256;  // FP32 partial sums of one 128-channel x 256-token tile
 constexpr int kMaxOutputPeers = 16;   // ranks whose buffers an epilogue can scatter to
 constexpr int kMaxSplitTiles = 128;  // output tiles of a K-split launch: the tile index takes 7 bits of a tag
 constexpr int kTransposeBytes = 16 * 32 * 2;  // an epilogue warp's 16-column chunk as BF16 [token][channel]
@@ -109,6 +112,10 @@ struct alignas(64) GemmParams {
     int n_tiles, k_blocks;  // 128-channel tiles, 128-deep K blocks
     int layout, num_experts, top_k;
     int splits;    // dense: K splits (>= 1)
+    // dense, 256-token tile: when shared_tiles > 0 every CTA runs whole_rounds whole tiles (tile = CTA + round x grid)
+    // and then an even share of the K blocks of the shared_tiles tiles that are left over; the CTA that holds the
+    // first K blocks of such a tile finishes it from the partial sums of the CTAs that hold the rest.
+    int whole_rounds, shared_tiles;
     int a_gathered;  // indexed: `a` is already [padded routes, k] in sorted order (tb_gather_rows ran first)
     int static_weights;      // 1: no kernel in flight on the stream writes weight / scale: they may be read before
                              //    griddepcontrol.wait returns
@@ -140,6 +147,8 @@ struct Unit {
     int kb0, kb1;    // K-block range
     int tile;        // dense tile index (slot of its partial sums in the split-K workspace)
     int split;
+    int part;        // shared tiles: 0 whole tile, 1 its first K blocks (finishes the tile), 2 later K blocks (publishes)
+    int partners;    // part 1: the CTAs after this one that hold the tile's other K blocks
     bool skip;       // test hook (GemmParams::only_split): the unit is left out by every role
 };
 
@@ -375,9 +384,28 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         total_units = prefix[p.num_experts] * n_groups;
     }
 
+    // Units of this CTA: every gridDim.x-th unit -- or, with shared tiles, an index into its whole rounds followed by
+    // the shared tiles its share of K blocks [share0, share1) touches.
+    int u_begin = blockIdx.x, u_step = gridDim.x, u_end = total_units;
+    [[maybe_unused]] int share0 = 0, share1 = 0;
+    auto share_begin = [&](int cta) {  // first K block (counted over all shared tiles) of a CTA's share
+        return static_cast<int>(static_cast<long long>(cta) * p.shared_tiles * p.k_blocks / gridDim.x);
+    };
+    if constexpr (kAccSets == 1) {
+        if (p.shared_tiles > 0) {
+            share0 = share_begin(blockIdx.x);
+            share1 = share_begin(blockIdx.x + 1);
+            u_begin = 0;
+            u_step = 1;
+            u_end = p.whole_rounds + (share1 > share0 ? (share1 - 1) / p.k_blocks - share0 / p.k_blocks + 1 : 0);
+        }
+    }
+
     auto decode = [&](int u) {
         Unit t;
         t.split = 0;
+        t.part = 0;
+        t.partners = 0;
         t.skip = false;
         t.kb0 = 0;
         t.kb1 = p.k_blocks;
@@ -385,6 +413,17 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         if (p.layout == kDense) {
             t.tile = p.div_splits.div(u);
             t.split = u - t.tile * p.splits;
+            [[maybe_unused]] int shared_index = -1;
+            if constexpr (kAccSets == 1) {
+                if (p.shared_tiles > 0) {
+                    if (u < p.whole_rounds) {
+                        t.tile = blockIdx.x + u * gridDim.x;
+                    } else {
+                        shared_index = share0 / p.k_blocks + (u - p.whole_rounds);
+                        t.tile = p.whole_rounds * gridDim.x + shared_index;
+                    }
+                }
+            }
             const int g = p.div_n_tiles.div(t.tile);
             t.nt = t.tile - g * n_groups;
             t.row0 = g * BM;
@@ -393,6 +432,17 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             t.kb0 = p.div_splits.div(t.split * p.k_blocks);
             t.kb1 = p.div_splits.div((t.split + 1) * p.k_blocks);
             t.skip = p.only_split != 0 && t.split != p.only_split - 1;
+            if constexpr (kAccSets == 1) {
+                if (shared_index >= 0) {  // this CTA's share covers K blocks [kb0, kb1) of the shared tile
+                    t.kb0 = max(0, share0 - shared_index * p.k_blocks);
+                    t.kb1 = min(p.k_blocks, share1 - shared_index * p.k_blocks);
+                    t.part = t.kb0 > 0 ? 2 : (t.kb1 < p.k_blocks ? 1 : 0);
+                    if (t.part == 1) {
+                        const int tile_end = (shared_index + 1) * p.k_blocks;
+                        while (share_begin(blockIdx.x + 1 + t.partners) < tile_end) ++t.partners;  // the last CTA's share ends with the last tile
+                    }
+                }
+            }
         } else {
             const int g = p.div_n_tiles.div(u);
             t.nt = u - g * n_groups;
@@ -433,10 +483,10 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             uint32_t phase = 0;
             [[maybe_unused]] uint32_t waited = 0;
             [[maybe_unused]] const uint32_t loop_begin = TB_CLOCK();
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            for (int u = u_begin; u < u_end && ok; u += u_step) {
                 const Unit t = decode(u);
                 if (t.skip) continue;
-                if (u == static_cast<int>(blockIdx.x)) TB_PHASE(14);
+                if (u == u_begin) TB_PHASE(14);
                 const uint8_t* codes =
                     p.weight + ((static_cast<long long>(t.expert) * p.n_tiles + t.nt) * p.k_blocks + t.kb0) * kBlockBytes;
                 // group scales: [E, K/128, n_pad, 8] bytes, 1 KB per (K block, channel tile); else a TMA box of the
@@ -449,7 +499,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
                     if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitWeightEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     waited += TB_CLOCK() - w0;
-                    if (kb == t.kb0 && u == static_cast<int>(blockIdx.x)) TB_PHASE(15);
+                    if (kb == t.kb0 && u == u_begin) TB_PHASE(15);
                     mbar_arrive_expect_tx(full, kWeightRawBytes);
                     bulk_load(stage, codes, kBlockBytes, full);
                     if constexpr (kGroupScales) {
@@ -486,13 +536,13 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 int rs = 0;
                 uint32_t phase = 0;
                 bool ok = true;
-                for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                for (int u = u_begin; u < u_end && ok; u += u_step) {
                     const Unit t = decode(u);
                     if (t.skip) continue;
                     int x = t.kb0 * 128;
                     for (int kb = t.kb0; kb < t.kb1; ++kb) {
                         if (!mbar_wait(empty, phase ^ 1u, abort_flag, kWaitTokenEmpty, 0, p.wait_cycles)) { ok = false; break; }
-                        if (dense && u == static_cast<int>(blockIdx.x) && kb == t.kb0) pdl_wait_prior_grid();
+                        if (dense && u == u_begin && kb == t.kb0) pdl_wait_prior_grid();
                         mbar_arrive_expect_tx(full, kActBytes);
                         tma_load_2d(stage, &p.map_a, x, t.row0, full);
                         x += 128;
@@ -507,7 +557,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             uint32_t phase = 0;
             const long long route_limit = p.rows * p.top_k;
             bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            for (int u = u_begin; u < u_end && ok; u += u_step) {
                 const Unit t = decode(u);
                 if (t.skip) continue;
                 // Source row of every tile row (-1 = padding), once per tile: route id / top_k.
@@ -553,7 +603,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             int rs = 0, bs = 0, acc = 0;
             uint32_t bphase = 0, tphase = 0, aphase = 0;
             [[maybe_unused]] uint32_t waited = 0, blocks = 0, loop_begin = 0;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            for (int u = u_begin; u < u_end && ok; u += u_step) {
                 const Unit t = decode(u);
                 if (t.skip) continue;
                 if constexpr (!kGroupScales) {
@@ -622,7 +672,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         int turn = first;  // blocks to skip until this team's next one
         bool ok = true;
         [[maybe_unused]] uint32_t waited_raw = 0, waited_empty = 0, blocks = 0, loop_begin = 0;
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        for (int u = u_begin; u < u_end && ok; u += u_step) {
             const Unit t = decode(u);
             if (t.skip) continue;
             for (int kb = t.kb0; kb < t.kb1; ++kb) {
@@ -709,7 +759,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         // one has ended, so the tags of a launch differ from those of every earlier one -- under CUDA-graph replay and
         // after a launch that gave up as well.  (The arrival releases, so the read before it cannot slip behind it.)
         uint32_t launch_seq = 0;
-        if (!kGroupScales && p.layout == kDense && p.splits > 1) {
+        if (!kGroupScales && p.layout == kDense && (p.splits > 1 || p.shared_tiles > 0)) {
             volatile uint32_t* const seq_slot = reinterpret_cast<volatile uint32_t*>(smem + L.misc + 8);
             if (warp == 0 && lane == 0) {
                 unsigned* const head = reinterpret_cast<unsigned*>(p.workspace);
@@ -729,7 +779,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         uint32_t aphase = 0;
         bool ok = true;
         const long long route_limit = p.rows * p.top_k;
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        for (int u = u_begin; u < u_end && ok; u += u_step) {
             const Unit t = decode(u);
             if (t.skip) continue;
             const float gs = p.global_scale[t.expert];
@@ -895,6 +945,34 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     uint32_t kept[kKept > 0 ? kKept * 8 : 1];
                     const uint32_t acc_addr = lane_base + acc * BM + col0;
                     const float* const scale_pair = my_scale + 2 * (lane & 3);
+                    // Shared tiles.  A CTA that holds later K blocks of a tile publishes the FP32 partial sums as they
+                    // come out of tensor memory -- register for register, so the thread that holds an element here holds
+                    // it there -- and raises its flag with the launch's tag; the CTA that holds the first K blocks waits
+                    // for the flags of the CTAs behind it that hold the rest (bounded) and adds their sums to its own
+                    // before it scales, in CTA order: always the same order of additions.
+                    uint4* const partial = reinterpret_cast<uint4*>(p.workspace + kEpochCells) +
+                        (static_cast<long long>(blockIdx.x) * kBalancedTileWords >> 2) + warp * (8 * 4 * 32) + lane;
+                    const uint32_t balanced_tag = (launch_seq + 1u) & 0x1FFFFFFu;
+                    if (t.part == 1) {
+                        if (warp == 0 && lane == 0) {
+                            const long long start = clock64();
+                            for (int q = 1; q <= t.partners; ++q) {
+                                const unsigned* const flag = reinterpret_cast<const unsigned*>(p.workspace) + kBalancedFlag0 + blockIdx.x + q;
+                                unsigned seen;
+                                for (uint32_t spin = 0;; ++spin) {
+                                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                                    if (seen == balanced_tag) break;
+                                    if ((spin & 15u) == 15u && (*abort_flag != 0 || clock64() - start > p.wait_cycles)) {
+                                        atomicCAS(const_cast<int*>(abort_flag), 0, kWaitSplit);
+                                        break;
+                                    }
+                                }
+                                if (*abort_flag != 0) break;
+                            }
+                        }
+                        named_barrier_sync(1, kEpilogueWarps * 32);
+                        if (*abort_flag != 0) { ok = false; break; }
+                    }
                     auto step = [&](auto chunk) {
                         constexpr int c = decltype(chunk)::value;
                         if (c * 16 < cols_valid) {  // warp-uniform
@@ -902,6 +980,26 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                             tmem_ld_16x256b_x2(acc_addr + c * 16, lo);
                             tmem_ld_16x256b_x2(acc_addr + c * 16 + (16u << 16), hi);
                             tmem_ld_wait_for(lo, hi);
+                            if (t.part == 1) {  // the partners' sums of the same registers (written by other SMs: not through L1)
+                                for (int q = 1; q <= t.partners; ++q) {
+                                    const uint4* const theirs = partial + (static_cast<long long>(q) * kBalancedTileWords >> 2) + c * 4 * 32;
+                                    const uint4 q0 = __ldcg(theirs), q1 = __ldcg(theirs + 32), q2 = __ldcg(theirs + 64), q3 = __ldcg(theirs + 96);
+                                    const uint32_t w[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                                            q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) {
+                                        lo[i] = __float_as_uint(__uint_as_float(lo[i]) + __uint_as_float(w[i]));
+                                        hi[i] = __float_as_uint(__uint_as_float(hi[i]) + __uint_as_float(w[8 + i]));
+                                    }
+                                }
+                            }
+                            if (t.part == 2) {
+                                __stcg(partial + (c * 4 + 0) * 32, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+                                __stcg(partial + (c * 4 + 1) * 32, make_uint4(lo[4], lo[5], lo[6], lo[7]));
+                                __stcg(partial + (c * 4 + 2) * 32, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+                                __stcg(partial + (c * 4 + 3) * 32, make_uint4(hi[4], hi[5], hi[6], hi[7]));
+                                return;
+                            }
                             const float2 s0 = *reinterpret_cast<const float2*>(scale_pair + c * 16);
                             const float2 s1 = *reinterpret_cast<const float2*>(scale_pair + c * 16 + 8);
                             auto pack = [](uint32_t x, uint32_t y, const float2& sc) {
@@ -926,6 +1024,16 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty(acc));
+                    if (t.part == 2) {  // published: every warp's stores, then the flag
+                        __threadfence();
+                        named_barrier_sync(1, kEpilogueWarps * 32);
+                        if (warp == 0 && lane == 0) {
+                            unsigned* const flag = reinterpret_cast<unsigned*>(p.workspace) + kBalancedFlag0 + blockIdx.x;
+                            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(balanced_tag) : "memory");
+                        }
+                        if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
+                        continue;
+                    }
                     // The output: lane -> token lane / 4 (and + 8) of a chunk, 8-channel word lane % 4 of its row.
                     const int tok = lane >> 2, part = lane & 3;
                     const int nv = t.nt * 128 + quad * 32 + part * 8;

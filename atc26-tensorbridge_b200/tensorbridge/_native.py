@@ -124,6 +124,8 @@ SYMBOLS = {
                                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tb_gather_rows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
                                       ctypes.c_void_p]),
+    "tb_moe_combine": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                      ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p]),
     "tb_peer_alloc": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]),
     "tb_peer_free": (ctypes.c_int, [ctypes.c_void_p]),
     "tb_ipc_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p]),

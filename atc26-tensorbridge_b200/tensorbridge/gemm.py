@@ -56,18 +56,20 @@ class PeerScatter:
     peer_out: object  # ctypes array of device pointers, one per rank
     world: int
 
-# FP32 split-K scratch per (device, stream): distinct streams never share partial sums.
-_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+# FP32 scratch per (device, stream, kind of launch): distinct streams never share partial sums, and launches with K
+# splits never share a buffer with launches that give every CTA an even share of K blocks (`use_stream_k = 1`), whose
+# partial sums a K-split launch could mistake for tags.
+_workspaces: dict[tuple[int, int, bool], torch.Tensor] = {}
 # Buffers that were replaced by larger ones.  A CUDA graph captured earlier on the stream still launches with the old
 # pointer, so the old buffer must stay allocated for as long as the process may replay that graph: buffers only ever
 # grow by appending, nothing is handed back to the allocator.
 _retired: list[torch.Tensor] = []
 
 
-def _workspace(device: torch.device, nbytes: int, stream: int) -> torch.Tensor | None:
+def _workspace(device: torch.device, nbytes: int, stream: int, even_shares: bool = False) -> torch.Tensor | None:
     """A scratch buffer of at least `nbytes` for `stream`, or None when one would have to be allocated while the
     stream is being captured into a CUDA graph."""
-    key = (device.index, stream)
+    key = (device.index, stream, even_shares)
     have = _workspaces.get(key)
     if have is not None and have.numel() * 4 >= nbytes:
         return have
@@ -83,7 +85,7 @@ def _workspace(device: torch.device, nbytes: int, stream: int) -> torch.Tensor |
 def reset_workspaces(device: int | None = None) -> None:
     """Zero the split-K scratch of `device` (all devices when None).  Needed only after `check_status()` reported a
     kernel that gave up waiting, if the same CUDA graph is to be replayed: eager launches number themselves afresh."""
-    for (index, _), buffer in _workspaces.items():
+    for (index, _, _), buffer in _workspaces.items():
         if device is None or index == device:
             buffer.zero_()
 
@@ -185,7 +187,7 @@ def _relaunch(call: _Call, device: torch.device) -> None:
     stream = _native.stream_ptr(index)
     cfg_ref = call.cfg_ref
     if call.need > 0:
-        workspace = _workspace(device, call.need, stream)
+        workspace = _workspace(device, call.need, stream, call.cfg.use_stream_k == 1)
         if workspace is None:
             cfg_ref = call.unsplit_cfg_ref
             args.workspace, args.workspace_bytes = None, 0
@@ -225,7 +227,7 @@ def _launch(a, a_scale, strides, weight_t, scale_t, global_scale, locks, out, ro
     stream = _native.stream_ptr(device.index)
     cfg_ref = call.cfg_ref
     if call.need > 0:
-        workspace = _workspace(device, call.need, stream)
+        workspace = _workspace(device, call.need, stream, call.cfg.use_stream_k == 1)
         if workspace is None:  # capturing without a buffer: run unsplit rather than allocate inside the capture
             cfg_ref = call.unsplit_cfg_ref
             args.workspace, args.workspace_bytes = None, 0

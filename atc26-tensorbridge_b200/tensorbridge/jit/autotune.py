@@ -37,9 +37,12 @@ def candidates(base: GemmConfig, m: int, layout: str, group_scales: bool) -> lis
         if bm != base.block_m and (bm >= min(m, tiles[-1]) or layout != "dense" or m > tiles[-1]) and bm in (base.block_m // 2, base.block_m * 2):
             out.append(dataclasses.replace(base, block_m=bm, num_stages=min(base.num_stages, 8 if bm >= 128 else 12)))
     if layout == "dense" and not group_scales:
-        for splits in {0, max(base.use_stream_k - 1, 0), base.use_stream_k + 1, base.use_stream_k * 2}:
-            if splits != base.use_stream_k and splits != 1:
-                out.append(dataclasses.replace(base, use_stream_k=splits))
+        if base.use_stream_k == 1:  # last round shared out in K blocks: the only alternative is whole tiles
+            out.append(dataclasses.replace(base, use_stream_k=0))
+        else:
+            for splits in {0, max(base.use_stream_k - 1, 0), base.use_stream_k + 1, base.use_stream_k * 2}:
+                if splits != base.use_stream_k and splits != 1:
+                    out.append(dataclasses.replace(base, use_stream_k=splits))
     for bridged in (2, 8):  # 8 only fits where the accumulators leave 256 columns of tensor memory
         if bridged == 2 or not group_scales or base.block_m <= 32:
             out.append(dataclasses.replace(base, stream_k_aligned=bridged))

@@ -30,7 +30,8 @@ class GemmConfig:
 
     On B200 they are read as: `block_m` token tile (16/32/64/128/256); `num_stages` depth of the weight ring (the token ring takes the
     rest of shared memory);
-    `use_stream_k` number of deterministic K splits of a dense GEMM (False/0/1 = none); `m_fast_tile_order`
+    `use_stream_k` dense GEMM: 0 whole tiles, 1 the tiles of the last partial round shared out in K blocks (256-token
+    tiles, more tiles than SMs; never picked by the rule), 2..16 that many deterministic K splits of every tile; `m_fast_tile_order`
     number of bridge teams that alternate K blocks (0/1, 2 or 4); `block_k` 128; `block_n` 128; `ctas_per_sm` 1; `stream_k_aligned` bridged FP8 weight
     tiles kept in tensor memory (2..8, 0 = default 4); `math_warpgroups` bridge warps / 4 (2 or 4).
     """

@@ -139,6 +139,31 @@ def _plan_native(x_q, x_scale, topk_ids, num_experts, world, placement, row_byte
     return send_counts, send_pos, send
 
 
+def plan_local(topk_ids: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Routes of one rank sorted by expert: int32 `counts[E]` and, per route, its position in expert order (int32
+    `[routes]`, -1 for ids outside `[0, E)`; routes of one expert keep their order).  The send plan of a world of
+    one: the dispatch plan kernel on CUDA (`E <= 1024`), torch ops elsewhere."""
+    ids = topk_ids.reshape(-1).contiguous()
+    if not ids.is_cuda:
+        flat = ids.to(torch.int64)
+        local = (flat >= 0) & (flat < num_experts)
+        keyed = torch.where(local, flat, torch.full_like(flat, num_experts))
+        order = torch.argsort(keyed, stable=True)
+        counts = torch.bincount(keyed, minlength=num_experts + 1)[:num_experts].to(torch.int32)
+        positions = torch.empty_like(order)
+        positions[order] = torch.arange(flat.numel(), device=flat.device)
+        return counts, torch.where(local, positions, torch.full_like(positions, -1)).to(torch.int32)
+    from tensorbridge import _native  # noqa: PLC0415
+    if ids.dtype not in (torch.int32, torch.int64):
+        ids = ids.to(torch.int64)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=ids.device)
+    positions = torch.empty(ids.numel(), dtype=torch.int32, device=ids.device)
+    with torch.cuda.device(ids.device):
+        _native.check(_native.load().tb_ep_plan(_native.stream_ptr(ids.device), ids.data_ptr(), int(ids.dtype == torch.int64),
+                                                ids.numel(), num_experts, 1, 0, counts.data_ptr(), positions.data_ptr(), None))
+    return counts, positions
+
+
 def _place_torch(recv, recv_counts, capacity, width, groups, fp8_dtype):
     world, e_local = recv_counts.shape
     device = recv.device

@@ -43,7 +43,11 @@ enum { TB_QUANT_PER_TOKEN = 0, TB_QUANT_GROUP_128 = 1 };
  *                      64 up) once tb_register_kernel has a kernel for them
  *   num_stages         depth of the weight ring (codes + scales, 9 KB a stage), rounded down to a multiple of the
  *                      bridge teams; the token ring takes what is left of shared memory, at most 8 stages
- *   use_stream_k       number of deterministic K splits of a dense GEMM (0 or 1 = none)
+ *   use_stream_k       dense GEMM: 0 = whole tiles; 1 = the tiles of the last, partial round are shared out in even
+ *                      shares of K blocks (256-token tiles, more tiles than SMs: the CTA with a tile's first K
+ *                      blocks finishes it from the FP32 partial sums of the others, added in a fixed order;
+ *                      launches it does not fit run whole tiles);
+ *                      2..16 = that many deterministic K splits of every tile
  *   m_fast_tile_order  bridge teams that alternate K blocks: 0/1 = one team, 2 or 4
  *   block_k            128
  *   block_n            128 (channels per unit of work = UMMA M)
@@ -91,8 +95,11 @@ int tb_num_sms(int device, int* num_sms);
  * tensorbridge/csrc/heuristics/sm90_rule.hpp:333-348. */
 int tb_select_config(const tb_problem* problem, tb_config* config);
 
-/* Bytes of scratch a dense launch with `config` needs for its K splits (0 without splits, or for a block_m the
- * library does not have): a 4 KB header and one 8-byte {partial sum, tag} word per element of every split.
+/* Bytes of scratch a dense launch with `config` needs (0 for whole-tile launches, or for a block_m the library does
+ * not have).  K splits (use_stream_k >= 2): a 4 KB header and one 8-byte {partial sum, tag} word per element of every
+ * split.  Shared last round (use_stream_k = 1): the header and one FP32 partial tile (128 KB) per CTA, counted for up
+ * to 256 SMs.  Do not hand one workspace to launches of both kinds: a partial sum left by a shared-round launch could be
+ * mistaken for the tag of a later K-split launch.
  * No counterpart in the reference, whose Stream-K tail adds into the BF16 output in place. */
 int64_t tb_workspace_bytes(int64_t m, int64_t n, const tb_config* config);
 
@@ -300,6 +307,15 @@ int tb_ep_place(void* stream, const void* recv, int64_t rows, int64_t row_bytes,
 
 /* dst[i] = index[i] >= 0 ? src[index[i]] : zeros, rows of `row_bytes` bytes (a multiple of 16). */
 int tb_gather_rows(void* stream, const void* src, const int32_t* index, int64_t rows, int64_t row_bytes, void* dst);
+
+/* out[t, :] = bf16(sum_j weights[t, j] * rows[index[t * top_k + j], :]) over BF16 rows of `width` channels (a multiple
+ * of 8; FP32 sums in slot order, so the result repeats from run to run).  `index` NULL: route t * top_k + j reads row
+ * t * top_k + j (the route-ordered output of an indexed grouped GEMM); a negative index adds nothing (a route whose
+ * expert lives on another rank).  `weights` FP32 [tokens, top_k].
+ * Stands in for the two vLLM helpers the reference calls after its down projection, moe_fused_mul_sum (indexed) and
+ * moe_unpermute (contiguous): tensorbridge/vllm_moe.py:377-379 and :407. */
+int tb_moe_combine(void* stream, const void* rows, const int32_t* index, const float* weights, int64_t tokens, int32_t top_k,
+                   int64_t width, void* out);
 
 /* ---- The same dispatch over peer memory: NVLink loads and stores between the GPUs of one node, no collective library,
  * no host read, no staging copy.  No counterpart in the reference (its overlap.py streams tokens into a masked buffer

@@ -100,6 +100,48 @@ def test_dense_split_k_is_deterministic_and_correct(splits, block_m):
     assert int(weight.locks.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("m,n,k,num_sms", [(1024, 6144, 1024, 0), (777, 6400, 1280, 0), (512, 640, 1024, 7),
+                                            (700, 384, 2048, 4), (2048, 1152, 512, 13)])
+def test_dense_even_k_block_shares(m, n, k, num_sms):
+    """`use_stream_k = 1` on the 256-token tile: every CTA takes an even share of all K blocks, and a tile cut between
+    two CTAs is finished by the first from the FP32 partial sums the second published.  Right against the oracle,
+    bit-identical from launch to launch (the two parts are always added in the same order), within an FP32 rounding of
+    the whole-tile launch -- and the launch did take the shared path (flags of the publishing CTAs carry its tag)."""
+    import ctypes
+    import tensorbridge as tb
+    from tensorbridge import _native as native
+    lib = native.load()
+    view, weight, q, s, wq, ws = _case(m, n, k, "exact", seed=m + k)
+    shared = native.Config(256, 4, 1, 4, 128, 128, 1, 4, 4)
+    whole = native.Config(256, 4, 0, 4, 128, 128, 1, 4, 4)
+    need = lib.tb_workspace_bytes(m, n, ctypes.byref(shared))
+    assert need > 0
+    workspace = torch.zeros(need // 4, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    tb.check_status()
+
+    def run(config):
+        out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device="cuda")
+        a = native.GemmArgs(q.data_ptr(), s.data_ptr(), 1, 0, weight.weight.data_ptr(), weight.scale.data_ptr(),
+                            weight.global_scale.data_ptr(), weight.locks.data_ptr(), workspace.data_ptr(), need,
+                            out.data_ptr(), m, n, k, native.BRIDGE_IDS["exact"], 0, 0, num_sms,
+                            native.status_words(0).data_ptr())
+        native.check(lib.tb_gemm_dense(stream, ctypes.byref(a), ctypes.byref(config)))
+        tb.check_status()
+        return out
+
+    outs = [run(shared) for _ in range(3)]
+    _check(outs[0], view, wq, ws, n, k)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    head = workspace.view(torch.int32)[:1024].cpu()
+    assert int(head[0]) == 3, "three launches numbered themselves"
+    assert int((head[16:] == 3).sum()) > 0, "no CTA published a partial tile: the launch ran whole tiles"
+    reference = run(whole)
+    difference = (outs[0].float() - reference.float()).abs()
+    assert float(difference.max()) <= float(reference.float().abs().max()) * 2 ** -7
+    assert float((difference > 0).float().mean()) < 0.2  # only the cut tiles can differ, by a rounding
+
+
 @pytest.mark.parametrize("num_sms", [0, 1])
 def test_split_k_wait_runs_out_reports_and_recovers(num_sms):
     """A bounded wait that runs out ends the launch with a status code instead of a hang.  Made to happen from the host:

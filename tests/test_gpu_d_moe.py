@@ -406,6 +406,107 @@ def test_moe_forward_custom_activation():
     assert float((a - b).norm() / a.norm()) <= 5e-3
 
 
+@pytest.mark.parametrize("tokens,top_k,width,indexed", [(1, 1, 8, False), (37, 4, 2048, False), (300, 8, 1536, True),
+                                                       (64, 2, 136, True)])
+def test_combine_routes_kernel(tokens, top_k, width, indexed):
+    """`tb_moe_combine` against the same sum in torch: FP32 multiply-adds in slot order, one BF16 rounding at the end;
+    routes with a negative index add nothing."""
+    from tensorbridge import vllm_moe
+    g = torch.Generator().manual_seed(tokens + width)
+    rows = torch.randn((tokens * top_k + 5, width), generator=g).bfloat16().cuda()
+    weights = torch.rand((tokens, top_k), generator=g).cuda()
+    index = None
+    if indexed:
+        index = torch.randint(-1, rows.size(0), (tokens, top_k), generator=g, dtype=torch.int32).cuda()
+    got = vllm_moe.combine_routes(rows, weights, None if index is None else index.reshape(-1))
+    source = rows[:tokens * top_k].view(tokens, top_k, width) if index is None else rows[index.clamp(min=0).long()]
+    want = torch.zeros((tokens, width), dtype=torch.float32, device="cuda")
+    for j in range(top_k):
+        term = torch.addcmul(want, source[:, j].float(), weights[:, j:j + 1])  # fused multiply-add, like the kernel
+        want = term if index is None else torch.where((index[:, j] >= 0).unsqueeze(1), term, want)
+    close = (got.float() - want.bfloat16().float()).abs() <= want.abs() * 2 ** -7 + 1e-30
+    assert bool(close.all())
+    assert float((got != want.bfloat16()).float().mean()) < 1e-3  # addcmul may not fuse exactly like fmaf
+
+
+@pytest.mark.parametrize("layout", ["indexed", "contiguous"])
+def test_vllm_style_moe_method_without_vllm(layout):
+    """The layer-level adapter: checkpoint tensors on a module -> `process_weights_after_loading` -> `apply(x, topk_weights,
+    topk_ids)`.  Its output is the weighted sum of what `moe_forward_*` returns for each route (checked against those
+    functions driven by hand), and agrees with a float reference of the whole layer to quantisation accuracy; with an
+    `expert_map` that hides half of the experts, the hidden routes add nothing."""
+    import tensorbridge as tb
+    from tensorbridge import serving, vllm_moe
+    _, v13, v2 = _layer(layout, "per_token")
+    p13, s13, g13, p2, s2, g2 = [], [], [], [], [], []
+    for e in range(E):
+        gate = orc.quantize_nvfp4(seeded_weight(I, H, seed=700 + e, std=0.05))
+        up = orc.quantize_nvfp4(seeded_weight(I, H, seed=800 + e, std=0.02))
+        down = orc.quantize_nvfp4(seeded_weight(H, I, seed=900 + e, std=0.05))
+        p13.append(np.concatenate([gate[0], up[0]])), s13.append(np.concatenate([gate[1], up[1]]))
+        g13.append(np.array([gate[2][0], up[2][0]], np.float32))
+        p2.append(down[0]), s2.append(down[1]), g2.append(down[2][0])
+    cuda = lambda xs, dt=None: torch.from_numpy(np.stack(xs)).cuda() if dt is None else torch.from_numpy(np.stack(xs)).cuda().view(dt)
+    layer = torch.nn.Module()
+    layer.w13_weight, layer.w13_weight_scale, layer.w13_weight_scale_2 = cuda(p13), cuda(s13, torch.float8_e4m3fn), cuda(g13)
+    layer.w2_weight, layer.w2_weight_scale = cuda(p2), cuda(s2, torch.float8_e4m3fn)
+    layer.w2_weight_scale_2 = torch.tensor(g2, dtype=torch.float32, device="cuda")
+    layer.w13_input_scale = torch.ones(1, device="cuda")
+    method = vllm_moe.TensorBridgeMoEMethod(TOP_K, E, layout=layout, checkpoint="modelopt", layer_name="layers.0.mlp")
+    method.process_weights_after_loading(layer)
+    assert not hasattr(layer, "w13_weight_scale_2") and not hasattr(layer, "w13_input_scale")
+    assert layer.w13_weight.dtype == torch.int32 and layer.tensorbridge_w2_locks.numel() == 1024
+
+    tokens = 29
+    rng = np.random.default_rng(8)
+    topk = np.stack([rng.choice(E, size=TOP_K, replace=False) for _ in range(tokens)])
+    ids = torch.from_numpy(topk).cuda()
+    weights = torch.from_numpy(rng.random((tokens, TOP_K), np.float32)).cuda()
+    x = seeded_activations(tokens, H, seed=31)
+    out = method.apply(layer, x.cuda(), weights, ids)
+    tb.check_status()
+    assert out.shape == (tokens, H) and out.dtype == torch.bfloat16
+
+    w13 = [orc.e4m3_decode(v["fp8"][:2 * I, :H]) * v["global_scale6"][0] for v in v13]
+    w2 = [orc.e4m3_decode(v["fp8"][:H, :I]) * v["global_scale6"][0] for v in v2]
+    xf = x.float().numpy()
+
+    def reference(keep):
+        ref = np.zeros((tokens, H), np.float32)
+        for t in range(tokens):
+            for j in range(TOP_K):
+                e = topk[t, j]
+                if keep(e):
+                    gu = xf[t] @ w13[e].T
+                    ref[t] += float(weights[t, j]) * ((gu[:I] / (1 + np.exp(-gu[:I])) * gu[I:]) @ w2[e].T)
+        return ref
+
+    ref = reference(lambda e: True)
+    assert np.linalg.norm(out.float().cpu().numpy() - ref) / np.linalg.norm(ref) <= 0.08
+    again = method.apply(layer, x.cuda(), weights, ids)
+    assert torch.equal(out, again)
+
+    # the same experts object serves a rank that holds only the even experts: ids go through expert_map, the others drop out
+    if layout == "indexed":
+        half = vllm_moe.make_experts(serving.NVFP4MoE(
+            w13=_take(method.experts.prepared.w13, slice(0, E, 2)), w2=_take(method.experts.prepared.w2, slice(0, E, 2)),
+            top_k=TOP_K, num_global_experts=E, dispatch_ranks=1, layout="indexed", configs=None))
+        expert_map = torch.full((E,), -1, dtype=torch.int64, device="cuda")
+        expert_map[0::2] = torch.arange(E // 2, device="cuda")
+        part = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+        half.apply(part, x.cuda(), weights, ids, expert_map=expert_map)
+        tb.check_status()
+        ref_half = reference(lambda e: e % 2 == 0)
+        assert np.linalg.norm(part.float().cpu().numpy() - ref_half) / np.linalg.norm(ref_half) <= 0.08
+
+
+def _take(experts, which):
+    """A subset of prepared experts (weights, scales and global scales sliced along the expert axis)."""
+    import dataclasses
+    return dataclasses.replace(experts, weight=experts.weight[which].contiguous(), scale=experts.scale[which].contiguous(),
+                               global_scale=experts.global_scale[which].contiguous())
+
+
 def test_vllm_style_linear_method_without_vllm():
     """`TensorBridgeLinearMethod` on a plain module: the loader's parameters are swapped for the kernel layout, a fused
     layer of two shards with different global scales is brought to a shared one, bias is added, leading dimensions kept."""
