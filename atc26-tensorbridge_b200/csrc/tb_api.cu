@@ -149,20 +149,20 @@ int pad128(long long x) { return ceil_div(x, 128) * 128; }
 bool valid_block_m(int bm) { return bm == 16 || bm == 32 || bm == 64 || bm == 128 || bm == 192 || bm == 256; }
 
 // Bytes left for the two rings once barriers, staging and routing tables are placed.
-int ring_room(int bm, int num_experts) {
-    return kSmemBudget - 1024 - static_cast<int>(tb::smem_layout(bm, 0, 0, num_experts).total);
+int ring_room(int bm, int num_experts, bool group_scales) {
+    return kSmemBudget - 1024 - static_cast<int>(tb::smem_layout(bm, 0, 0, num_experts, group_scales).total);
 }
 
 // Token ring depth that goes with a weight ring of `w_stages`: what is left, at most 8.
-int token_stages_for(int bm, int w_stages, int num_experts) {
-    const int room = ring_room(bm, num_experts) - w_stages * (tb::kBlockBytes + tb::kBlockScaleBytes);
+int token_stages_for(int bm, int w_stages, int num_experts, bool group_scales) {
+    const int room = ring_room(bm, num_experts, group_scales) - w_stages * (tb::kBlockBytes + tb::kBlockScaleBytes);
     return std::min(room / (bm * 128), 8);
 }
 
 // Weight ring depth of the rule: leave the token ring 8 stages for small token tiles, 6 at 128 and 5 at 256 tokens.
-int pick_weight_stages(int bm, int num_experts) {
+int pick_weight_stages(int bm, int num_experts, bool group_scales) {
     const int token_stages = bm <= 64 ? 8 : (bm == 128 ? 6 : 5);
-    const int room = ring_room(bm, num_experts) - token_stages * bm * 128;
+    const int room = ring_room(bm, num_experts, group_scales) - token_stages * bm * 128;
     const int fit = std::min(room / (tb::kBlockBytes + tb::kBlockScaleBytes), tb::kMaxRawStages);
     return std::max(4, fit / 4 * 4);  // a multiple of every team count (1, 2, 4): see the ring rule in run_gemm
 }
@@ -241,7 +241,7 @@ int rule(const tb_problem& pr, tb_config* cfg) {
     // Eight bridged tiles where two teams feed a split-K tile (measured better on the narrow shapes, equal elsewhere).
     const int bridged = std::min((!wide_bridge && splits > 1 && bm <= 128) ? 8 : 4, tb::max_bridged_stages(bm, pr.group_scales != 0));
     cfg->block_m = bm;
-    cfg->num_stages = pick_weight_stages(bm, pr.layout == TB_LAYOUT_DENSE ? 0 : pr.num_experts);
+    cfg->num_stages = pick_weight_stages(bm, pr.layout == TB_LAYOUT_DENSE ? 0 : pr.num_experts, pr.group_scales != 0);
     cfg->use_stream_k = splits > 1 ? splits : 0;
     cfg->m_fast_tile_order = wide_bridge ? 4 : 2;
     cfg->block_k = 128;
@@ -425,11 +425,11 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
     if (p.w_stages < ring_teams || p.bridged_stages < ring_teams || p.w_stages < 2 || p.bridged_stages < 2)
         return fail(TB_ERR_INVALID, "ring depths (num_stages %d, stream_k_aligned %d) must hold at least one stage per bridge team (%d) and two in all",
                     cfg->num_stages, cfg->stream_k_aligned, ring_teams);
-    p.a_stages = token_stages_for(bm, p.w_stages, experts);
+    p.a_stages = token_stages_for(bm, p.w_stages, experts, a->group_scales != 0);
     if (p.a_stages < 2)
         return fail(TB_ERR_INVALID, "num_stages %d leaves no room for two %d-token stages in %d bytes of shared memory",
                     p.w_stages, bm, std::min(kSmemBudget, info.smem_optin));
-    const tb::SmemLayout L = tb::smem_layout(bm, p.w_stages, p.a_stages, experts);
+    const tb::SmemLayout L = tb::smem_layout(bm, p.w_stages, p.a_stages, experts, a->group_scales != 0);
     // Slack for the 1024-byte alignment of the tiles; never less than half of an SM's shared memory, so that two
     // CTAs (of this launch, or of launches chained by PDL) cannot share an SM and wait for each other's tensor memory.
     const size_t smem = std::max<size_t>(L.total + 1024, 116 * 1024);

@@ -186,10 +186,14 @@ __host__ __device__ constexpr int min_kernel_registers(int bm, bool group_scales
 template <int kValue> struct IntC { static constexpr int value = kValue; };
 
 struct SmemLayout {
-    uint32_t tokens, token_stage, weights, weight_stage, barriers, misc, ids, epi, transpose, prefix, total;
+    uint32_t tokens, token_stage, weights, weight_stage, barriers, misc, ids, epi, transpose, group_scales, prefix, total;
 };
 
-__host__ __device__ inline SmemLayout smem_layout(int bm, int w_stages, int a_stages, int num_experts) {
+// [1,128] activation scales are staged in shared memory for kScaleChunk K blocks at a time, per epilogue warp as
+// [K block][token column of the warp], so that a K block costs the warp broadcast reads and no global load.
+constexpr int kScaleChunk = 16;
+
+__host__ __device__ inline SmemLayout smem_layout(int bm, int w_stages, int a_stages, int num_experts, bool group_scales = false) {
     SmemLayout l;
     l.tokens = 0;  // swizzled tiles first: every stage starts on a 1024-byte boundary
     l.token_stage = bm * 128;
@@ -200,7 +204,8 @@ __host__ __device__ inline SmemLayout smem_layout(int bm, int w_stages, int a_st
     l.ids = l.misc + 64;
     l.epi = l.ids + 256 * 4;  // per epilogue warp: BM scales + BM output rows
     l.transpose = l.epi + 4 * bm * 8;  // per lane quadrant: bm scales + bm rows, split between its column groups
-    l.prefix = l.transpose + epilogue_warps(bm) * staged_chunks(bm) * kTransposeBytes;  // per warp: chunks of 16 tokens x 32 channels of BF16
+    l.group_scales = l.transpose + epilogue_warps(bm) * staged_chunks(bm) * kTransposeBytes;  // per warp: chunks of 16 tokens x 32 channels of BF16
+    l.prefix = l.group_scales + (group_scales ? 4 * bm * kScaleChunk * 4 : 0);  // per lane quadrant: kScaleChunk x bm floats
     l.total = l.prefix + (num_experts > 0 ? (3 * num_experts + 4) * 4 : 0);
     return l;
 }
@@ -253,7 +258,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
     // The swizzled tiles need 1024-byte alignment of their shared addresses.
     const uint32_t base_u32 = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
     uint8_t* smem = smem_unaligned + (base_u32 - smem_u32(smem_unaligned));
-    const SmemLayout L = smem_layout(BM, p.w_stages, p.a_stages, p.num_experts);
+    const SmemLayout L = smem_layout(BM, p.w_stages, p.a_stages, p.num_experts, kGroupScales);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int WS = p.w_stages, AS = p.a_stages, BS = p.bridged_stages;
@@ -830,45 +835,53 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             __syncwarp();
 
             if constexpr (kGroupScales) {
-                // Promote each 128-deep partial with its [1,128] activation scale in registers.  The scales of the next
-                // two K blocks are in flight (one or two columns per lane) while the current block is consumed.
+                // Promote each 128-deep partial with its [1,128] activation scale in registers.  The scales of
+                // kScaleChunk K blocks at a time are staged in shared memory as [K block][column of this warp]: a
+                // lane fetches them for its one or two columns (independent loads, one round trip per chunk), and a
+                // K block then reads them with broadcast loads.
                 const int n = t.nt * 128 + n_local;
                 const bool n_ok = n < p.n;
                 constexpr int kPer = (kCols + 31) / 32;
                 float total[kCols];
 #pragma unroll
                 for (int c = 0; c < kCols; ++c) total[c] = 0.f;
-                float next[kPer], after[kPer];
-                auto fetch = [&](int kb, float (&dst)[kPer]) {
+                float* const staged = reinterpret_cast<float*>(smem + L.group_scales) + (quad * BM + cgroup * kCols) * kScaleChunk;
+                const float* scale_row[kPer];  // first scale of this lane's columns (null: no such row)
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) {
+                    const int c = j * 32 + lane;
+                    long long in_row = -1;
+                    if (c < kCols) {
+                        const int i = col0 + c;
+                        if (indexed) {
+                            const long long id = p.sorted_ids[t.row0 + i];
+                            if (id >= 0 && id < route_limit) in_row = id / p.top_k;
+                        } else if (i < t.rows_valid) {
+                            in_row = t.row0 + i;
+                        }
+                    }
+                    scale_row[j] = in_row >= 0 ? p.a_scale + in_row * p.a_scale_stride_m : nullptr;
+                }
+                auto stage_scales = [&](int kb) {  // K blocks kb .. kb + kScaleChunk - 1 of the tile
+                    __syncwarp();
 #pragma unroll
                     for (int j = 0; j < kPer; ++j) {
                         const int c = j * 32 + lane;
-                        float sv = 0.f;
-                        if (c < kCols && kb < t.kb1) {
-                            const int i = col0 + c;
-                            long long in_row = -1;
-                            if (indexed) {
-                                const long long id = p.sorted_ids[t.row0 + i];
-                                if (id >= 0 && id < route_limit) in_row = id / p.top_k;
-                            } else if (i < t.rows_valid) {
-                                in_row = t.row0 + i;
-                            }
-                            if (in_row >= 0) sv = p.a_scale[in_row * p.a_scale_stride_m + kb * p.a_scale_stride_k];
-                        }
-                        dst[j] = sv;
-                    }
-                };
-                fetch(t.kb0, next);
-                fetch(t.kb0 + 1, after);
-                for (int kb = t.kb0; kb < t.kb1 && ok; ++kb) {
-                    __syncwarp();
+                        if (c < kCols) {
+                            float sv[kScaleChunk];
 #pragma unroll
-                    for (int j = 0; j < kPer; ++j) {
-                        if (j * 32 + lane < kCols) my_scale[j * 32 + lane] = next[j];
-                        next[j] = after[j];
+                            for (int g = 0; g < kScaleChunk; ++g)
+                                sv[g] = (scale_row[j] != nullptr && kb + g < t.kb1) ? scale_row[j][(kb + g) * p.a_scale_stride_k] : 0.f;
+#pragma unroll
+                            for (int g = 0; g < kScaleChunk; ++g) staged[g * kCols + c] = sv[g];
+                        }
                     }
                     __syncwarp();
-                    fetch(kb + 2, after);
+                };
+                for (int kb = t.kb0; kb < t.kb1 && ok; ++kb) {
+                    const int local = (kb - t.kb0) & (kScaleChunk - 1);
+                    if (local == 0) stage_scales(kb);
+                    const float* const block_scale = staged + local * kCols;
                     if (!mbar_wait(acc_full(acc), aphase, abort_flag, kWaitAccFull, 0, p.wait_cycles)) { ok = false; break; }
                     tc_fence_after_sync();
 #pragma unroll
@@ -879,7 +892,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         tmem_ld_wait();
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {  // two packed FP32 multiply-adds per four columns
-                            const float4 s4 = *reinterpret_cast<const float4*>(my_scale + c * 32 + j4 * 4);
+                            const float4 s4 = *reinterpret_cast<const float4*>(block_scale + c * 32 + j4 * 4);
                             const uint32_t* vv = &v[j4 >> 2][(j4 & 3) * 4];
                             float* tt = &total[c * 32 + j4 * 4];
                             fma2(tt[0], tt[1], __uint_as_float(vv[0]), __uint_as_float(vv[1]), s4.x, s4.y);
@@ -893,7 +906,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         tmem_ld_wait();
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 s4 = *reinterpret_cast<const float4*>(my_scale + c16 + j4 * 4);
+                            const float4 s4 = *reinterpret_cast<const float4*>(block_scale + c16 + j4 * 4);
                             float* tt = &total[c16 + j4 * 4];
                             tt[0] = fmaf(__uint_as_float(v[j4 * 4 + 0]), s4.x, tt[0]);
                             tt[1] = fmaf(__uint_as_float(v[j4 * 4 + 1]), s4.y, tt[1]);
