@@ -674,17 +674,14 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         const uint32_t a_lane = tmem_base + kAccCols + (static_cast<uint32_t>(r & ~31) << 16);
         int rs = first % WS, bs = first % BS;
         uint32_t rphase = (first / WS) & 1, bphase = (first / BS) & 1;
-        int turn = first;  // blocks to skip until this team's next one
+        int turn = first;  // blocks of the coming unit that belong to the teams before this one's next block
         bool ok = true;
         [[maybe_unused]] uint32_t waited_raw = 0, waited_empty = 0, blocks = 0, loop_begin = 0;
         for (int u = u_begin; u < u_end && ok; u += u_step) {
             const Unit t = decode(u);
             if (t.skip) continue;
-            for (int kb = t.kb0; kb < t.kb1; ++kb) {
-                if (kTurns > 1) {
-                    if (turn != 0) { --turn; continue; }
-                    turn = kTurns - 1;
-                }
+            int kb = t.kb0 + turn;
+            for (; kb < t.kb1; kb += kTurns) {  // this team's blocks only
                 // The tensor-memory stores below are warp-wide instructions: the warp must agree on every wait's outcome.
                 [[maybe_unused]] const uint32_t w0 = TB_CLOCK();
                 if (!__all_sync(0xffffffffu, mbar_wait(w_full(rs), rphase, abort_flag, kWaitWeightFull, 0, p.wait_cycles))) { ok = false; break; }
@@ -738,6 +735,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 bs += kTurns;
                 if (bs >= BS) { bs -= BS; bphase ^= 1u; }
             }
+            turn = kb - t.kb1;  // what is left of the stride carries into the next unit
         }
         if (warp == kEpilogueWarps && lane == 0) { TB_REPORT(4, TB_CLOCK() - loop_begin); TB_REPORT(5, waited_raw); TB_REPORT(6, waited_empty); }
     } else {
