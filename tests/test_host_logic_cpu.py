@@ -140,3 +140,36 @@ def test_nvrtc_build_and_disk_cache(tmp_path, monkeypatch):
     broken = dataclasses.replace(source, source=source.source.replace("gemm_body", "no_such_body"))
     with pytest.raises(RuntimeError, match="NVRTC failed"):
         compiler.build(broken)
+
+
+def test_local_route_plan_and_moe_support_check():
+    """Host side of the MoE adapter: routes sorted by expert (torch path of `parallel.plan_local`) against a brute-force
+    stable sort, the scatter table built from it, and the support check's reasons on a duck-typed layer."""
+    import types
+    import torch
+    from tensorbridge import parallel, vllm_moe
+    g = torch.Generator().manual_seed(4)
+    experts = 6
+    ids = torch.randint(-1, experts + 1, (11, 3), generator=g)  # -1 and `experts` are routes of experts held elsewhere
+    counts, positions = parallel.plan_local(ids, experts)
+    flat = ids.reshape(-1).tolist()
+    order = sorted((i for i, e in enumerate(flat) if 0 <= e < experts), key=lambda i: (flat[i], i))
+    want = [-1] * len(flat)
+    for rank, route in enumerate(order):
+        want[route] = rank
+    assert positions.tolist() == want
+    assert counts.tolist() == [sum(1 for e in flat if e == x) for x in range(experts)]
+    offsets, scatter = vllm_moe.prepare_scatter(ids, experts)
+    assert scatter.shape == ids.shape and offsets.tolist() == [0] + torch.cumsum(counts, 0).tolist()
+
+    assert vllm_moe.uses_fused_silu("silu") and vllm_moe.uses_fused_silu("SiLU")
+    assert not vllm_moe.uses_fused_silu("gelu") and not vllm_moe.uses_fused_silu("silu", swiglu_limit=7.0)
+    layer = types.SimpleNamespace(moe_config=types.SimpleNamespace(in_dtype=torch.bfloat16, hidden_dim=2048,
+                                                                   intermediate_size_per_partition=1536))
+    reason = vllm_moe.unsupported_moe_reason(layer)
+    if not torch.cuda.is_available():
+        assert reason is not None and "Blackwell" in reason
+    with pytest.raises(ValueError):
+        vllm_moe.TensorBridgeMoEMethod(8, 128, checkpoint="gguf")
+    with pytest.raises(ValueError):
+        vllm_moe.make_experts(None, activation="gelu")  # a separate activation needs its function
