@@ -60,8 +60,8 @@ constexpr int kBarrierBytes = 832;     // 4 * 16 + 2 * 8 + 2 * 8 + 1 barriers of
 // Epilogue warps of a token tile: four cover the 128 tensor-memory lanes; from 64 tokens up a second set of four takes
 // the other half of the columns (halves the accumulator registers per thread and the time to drain a tile).
 __host__ __device__ constexpr int epilogue_warps(int bm) { return bm >= 64 ? 8 : 4; }
-// Threads of a CTA: epilogue + bridge (8 or 16) + weight producer + activation producer + two MMA warps.
-__host__ __device__ constexpr int gemm_threads(int bm, int bridge_warps) { return (epilogue_warps(bm) + bridge_warps + 4) * 32; }
+// Threads of a CTA: epilogue + bridge (8 or 16) + weight producer + activation producer + MMA warps.
+__host__ __device__ constexpr int gemm_threads(int bm, int bridge_warps) { return (epilogue_warps(bm) + bridge_warps + 3) * 32; }
 
 enum Layout : int { kDense = 0, kIndexed = 1, kContiguous = 2, kMasked = 3 };
 
@@ -239,8 +239,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
     static_assert(kCols % 16 == 0, "an epilogue warp drains whole 16-column chunks");
     constexpr int kWeightWarp = kEpilogueWarps + kBridgeWarps;
     constexpr int kActWarp = kWeightWarp + 1;
-    constexpr int kMmaWarp = kActWarp + 1;  // issues the even K blocks of every unit (and owns the tensor memory)
-    constexpr int kMmaWarp2 = kMmaWarp + 1;  // issues the odd ones
+    constexpr int kMmaWarp = kActWarp + 1;
     // The bridge warps form kBridgeGroups teams.  Team g converts the K blocks g, g + kTurns, ...: the fixed latency
     // of one block's hand-over (waits, fences, arrive) overlaps the conversion of the next blocks by the other teams.
     // A team is a multiple of four warps because warp w reaches only tensor-memory lanes 32 * (w % 4) .. +31.
@@ -277,7 +276,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L.misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc + 4);
-    const uint32_t issue_seq = base_u32 + L.misc + 12;  // K blocks of the CTA whose MMAs have been issued (the two MMA warps take turns)
     int* ids = reinterpret_cast<int*>(smem + L.ids);
     int* prefix = reinterpret_cast<int*>(smem + L.prefix);  // [E + 1] exclusive prefix of M blocks
     int* row_base = prefix + p.num_experts + 1;             // [E]
@@ -301,19 +299,14 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         fence_barrier_init();
     } else if (warp == kActWarp) {
         // Every other barrier slot, used or not, one per lane and pass: arrival counts by slot range.
-        constexpr int kAccFull0 = 4 * kMaxRawStages + 2 * kMaxBridgedStages, kDrain = kAccFull0 + 2 * kMaxAccSets;
-        constexpr int kSlots = kDrain + 1;
-        static_assert(kSlots * 8 <= kBarrierBytes, "barrier slots outgrew their room");
+        constexpr int kSlots = 4 * kMaxRawStages + 2 * kMaxBridgedStages + 2 * kMaxAccSets + 1;
         for (int slot = 2 * kMaxRawStages + lane; slot < kSlots; slot += 32) {
-            uint32_t count = 1u;  // a_empty, br_empty: one arrival (expect_tx or a commit)
+            uint32_t count = 1u;  // a_empty, br_empty, acc_full, drain: one arrival (expect_tx or a commit)
             if (slot < 3 * kMaxRawStages) count = gather ? 32u : 1u;                                             // a_full
             else if (slot >= 4 * kMaxRawStages && slot < 4 * kMaxRawStages + kMaxBridgedStages) count = kArrivals;  // br_full
-            else if (slot >= kAccFull0 && slot < kAccFull0 + kMaxAccSets) count = kGroupScales ? 1u : 2u;  // acc_full: the issuing warp of a block, or both warps' parts of a unit
-            else if (slot >= kAccFull0 + kMaxAccSets && slot < kDrain) count = kEpilogueWarps;  // acc_empty
-            else if (slot == kDrain) count = 2u;  // both MMA warps when the CTA unwinds
+            else if (slot >= 4 * kMaxRawStages + 2 * kMaxBridgedStages + kMaxAccSets && slot < kSlots - 1) count = kEpilogueWarps;  // acc_empty
             mbar_init(bar0 + 8u * slot, count);
         }
-        if (lane == 0) *reinterpret_cast<volatile uint32_t*>(smem + L.misc + 12) = 0u;
         fence_barrier_init();
     }
     // Tensor-memory columns of this CTA: accumulators + bridged ring, rounded up to a power of two (at least 32).
@@ -345,7 +338,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
     // out (and pulled into the instruction cache) everything the load needs.
     const bool dense = p.layout == kDense;
     const bool early = dense && ((p.static_weights != 0 && warp >= kEpilogueWarps && warp <= kWeightWarp) ||
-                                 warp == kMmaWarp || warp == kMmaWarp2 || (warp == kActWarp && !gather));
+                                 warp == kMmaWarp || (warp == kActWarp && !gather));
     if (!early) pdl_wait_prior_grid();
     if (threadIdx.x == 0) TB_PHASE(2);
 
@@ -599,71 +592,30 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
-    } else if (warp >= kMmaWarp) {
+    } else if (warp == kMmaWarp) {
         // =========================== MMA issue ===========================
-        // Two warps, one thread each: the first issues the even K blocks of every unit, the second the odd ones.  A
-        // block costs its issuing thread a few hundred cycles of waits, fence, four tcgen05.mma, commits and ring
-        // arithmetic whatever the tile (with every MMA taken out, a launch of 16 tokens was 0.9 us faster, no more):
-        // below 256 tokens that, not the tensor pipe, set the pace of the K loop.  With two threads one waits for its
-        // operands and does its arithmetic while the other issues.  The blocks still go to the tensor core in order --
-        // the accumulator adds them up in issue order, and results must not depend on timing: `issue_seq` in shared
-        // memory counts the blocks issued, a thread issues block g when the count is g and then stores g + 1.
-        // Ring positions follow from the same count, so each thread works them out for its own blocks.  With
-        // per-token scales both warps complete a unit's acc_full, each with a commit behind its last block of the unit
-        // (a plain arrival, once the unit's first block is out, from a warp that had none); with [1,128] scales every
-        // block has its own accumulator set and acc_full.
-        // Descriptors advance by additions: the B operand (activation tile, K-major, 128-byte swizzle) moves by the
-        // stage size, the A operand by 32 tensor-memory columns per bridged stage.
+        // One thread runs the whole loop.  Descriptors advance by additions: the B operand (activation tile, K-major,
+        // 128-byte swizzle) moves by the stage size, the A operand by 32 tensor-memory columns per bridged stage.
         constexpr uint32_t idesc = umma_idesc_e4m3(128, BM);
-        const int which = warp - kMmaWarp;
         bool ok = true;
         if (elect_one()) {
             const uint64_t b_desc0 = umma_desc_k_sw128(tokens0_u32);
             const uint64_t b_step = L.token_stage >> 4;
             const uint32_t a_addr0 = tmem_base + kAccCols;
-            uint32_t issued = 0;  // K blocks of the CTA before the current unit: block g sits in stage g % depth of each ring
-            uint32_t units_done = 0;
+            uint64_t b_desc = b_desc0;
+            uint32_t a_addr = a_addr0;
+            uint32_t t_full = a_full(0), t_empty = a_empty(0), b_full = br_full(0), b_empty = br_empty(0);
+            int rs = 0, bs = 0, acc = 0;
+            uint32_t bphase = 0, tphase = 0, aphase = 0;
             [[maybe_unused]] uint32_t waited = 0, blocks = 0, loop_begin = 0;
             for (int u = u_begin; u < u_end && ok; u += u_step) {
                 const Unit t = decode(u);
                 if (t.skip) continue;
-                const int len = t.kb1 - t.kb0;
-                const uint32_t g = issued + which;  // this warp's first block of the unit
-                int rs = static_cast<int>(g % AS), bs = static_cast<int>(g % BS);
-                uint32_t tphase = (g / AS) & 1u, bphase = (g / BS) & 1u;
-                uint64_t b_desc = b_desc0 + rs * b_step;
-                uint32_t t_full = a_full(rs), t_empty = a_empty(rs), b_full = br_full(bs), b_empty = br_empty(bs);
-                uint32_t a_addr = a_addr0 + bs * kTileCols;
-                int acc;
-                uint32_t aphase;
-                if constexpr (kGroupScales) {
-                    acc = static_cast<int>(g % kAccSets);
-                    aphase = (g / kAccSets) & 1u;
-                } else {
-                    acc = static_cast<int>(units_done % kAccSets);
-                    aphase = (units_done / kAccSets) & 1u;
-                    if (which == 0) {
-                        if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty, 0, p.wait_cycles)) { ok = false; break; }
-                    }
+                if constexpr (!kGroupScales) {
+                    if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty, 0, p.wait_cycles)) { ok = false; break; }
+                    tc_fence_after_sync();
                 }
-                // Spins (bounded) until `count` blocks of the CTA have been issued.
-                auto wait_issued = [&](uint32_t count) {
-                    const long long start = clock64();
-                    for (uint32_t spin = 1;; ++spin) {
-                        uint32_t seen;
-                        asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(issue_seq) : "memory");
-                        if (seen >= count) return true;
-                        if ((spin & 63u) == 0u) {
-                            if (*abort_flag != 0) return false;
-                            if (clock64() - start > p.wait_cycles) {
-                                atomicCAS(const_cast<int*>(abort_flag), 0, kWaitAccEmpty);
-                                return false;
-                            }
-                        }
-                    }
-                };
-                uint32_t my_block = g;  // position of this warp's next block in the CTA's sequence
-                for (int kb = t.kb0 + which; kb < t.kb1; kb += 2) {
+                for (int kb = t.kb0; kb < t.kb1; ++kb) {
                     if constexpr (kGroupScales) {
                         if (!mbar_wait(acc_empty(acc), aphase ^ 1u, abort_flag, kWaitAccEmpty, 0, p.wait_cycles)) { ok = false; break; }
                     }
@@ -673,10 +625,7 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                         if (!tokens_in && !mbar_wait(t_full, tphase, abort_flag, kWaitTokenFull, 0, p.wait_cycles)) { ok = false; break; }
                         if (!bridged_in && !mbar_wait(b_full, bphase, abort_flag, kWaitBridgedFull, 0, p.wait_cycles)) { ok = false; break; }
                     }
-                    if (which == 0) {
-                        if (blocks++ == 0) { loop_begin = TB_CLOCK(); TB_PHASE(5); } else { waited += TB_CLOCK() - w0; }
-                    }
-                    if (!wait_issued(my_block)) { ok = false; break; }  // this block's turn
+                    if (blocks++ == 0) { loop_begin = TB_CLOCK(); TB_PHASE(5); } else { waited += TB_CLOCK() - w0; }
                     tc_fence_after_sync();
                     if (gather) fence_proxy_async_smem();
                     const uint32_t d_addr = tmem_base + acc * BM;
@@ -687,49 +636,31 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     }
                     umma_commit(b_empty);
                     umma_commit(t_empty);
+                    if (kGroupScales || kb == t.kb1 - 1) umma_commit(acc_full(acc));
+                    b_desc += b_step; t_full += 8; t_empty += 8;
+                    if (++rs == AS) { rs = 0; tphase ^= 1u; b_desc = b_desc0; t_full = a_full(0); t_empty = a_empty(0); }
+                    a_addr += kTileCols; b_full += 8; b_empty += 8;
+                    if (++bs == BS) { bs = 0; bphase ^= 1u; a_addr = a_addr0; b_full = br_full(0); b_empty = br_empty(0); }
                     if constexpr (kGroupScales) {
-                        umma_commit(acc_full(acc));
-                        acc += 2;
-                        if (acc >= kAccSets) { acc -= kAccSets; aphase ^= 1u; }
-                        if (acc >= kAccSets) { acc -= kAccSets; aphase ^= 1u; }  // a single set wraps twice
+                        if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
                     }
-                    tc_fence_before_sync();
-                    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(issue_seq), "r"(my_block + 1u) : "memory");
-                    my_block += 2;
-                    rs += 2; b_desc += 2 * b_step; t_full += 16; t_empty += 16;
-                    while (rs >= AS) { rs -= AS; tphase ^= 1u; b_desc -= AS * b_step; t_full -= 8 * AS; t_empty -= 8 * AS; }
-                    bs += 2; a_addr += 2 * kTileCols; b_full += 16; b_empty += 16;
-                    while (bs >= BS) { bs -= BS; bphase ^= 1u; a_addr -= BS * kTileCols; b_full -= 8 * BS; b_empty -= 8 * BS; }
                 }
-                if (!ok) break;
                 if constexpr (!kGroupScales) {
-                    // this warp's share of the unit is issued: a commit behind its blocks, or a plain arrival if it had none
-                    if (which < len) {
-                        umma_commit(acc_full(acc));
-                    } else {
-                        if (!wait_issued(issued + 1u)) { ok = false; break; }  // not before the unit's only block is out
-                        mbar_arrive(acc_full(acc));
-                    }
+                    if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
                 }
-                issued += static_cast<uint32_t>(len);
-                ++units_done;
             }
-            if (which == 0) {
-                TB_PHASE(6);
-                TB_REPORT(2, TB_CLOCK() - loop_begin);
-                TB_REPORT(3, waited);
-                TB_REPORT(7, blocks);
-            }
+            TB_PHASE(6);
+            TB_REPORT(2, TB_CLOCK() - loop_begin);
+            TB_REPORT(3, waited);
+            TB_REPORT(7, blocks);
         }
         __syncwarp();
         // When unwinding, MMAs may still be running: wait (bounded) for them before the TMEM is released.
         if (*abort_flag != 0) {
             if (lane == 0) umma_commit(drain_bar);
             __syncwarp();
-            if (which == 0) {
-                const long long start = clock64();
-                while (!mbar_try_wait(drain_bar, 0) && clock64() - start < (1ll << 26)) {}
-            }
+            const long long start = clock64();
+            while (!mbar_try_wait(drain_bar, 0) && clock64() - start < (1ll << 26)) {}
         }
     } else if (warp >= kEpilogueWarps) {
         // =========================== bridge ===========================

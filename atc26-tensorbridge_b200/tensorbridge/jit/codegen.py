@@ -73,7 +73,7 @@ class KernelPoint:
 
     @property
     def threads(self) -> int:
-        return ((8 if self.block_m >= 64 else 4) + self.bridge_warps + 4) * 32
+        return ((8 if self.block_m >= 64 else 4) + self.bridge_warps + 3) * 32
 
 
 @dataclasses.dataclass(frozen=True)

@@ -105,7 +105,7 @@ def test_codegen_points_and_validation():
     from tensorbridge import GemmConfig
     from tensorbridge.jit import codegen
     aot = codegen.kernel_point(GemmConfig(block_m=256, m_fast_tile_order=4, math_warpgroups=4), "exact")
-    assert codegen.is_ahead_of_time(aot) and aot.threads == (8 + 16 + 4) * 32
+    assert codegen.is_ahead_of_time(aot) and aot.threads == (8 + 16 + 3) * 32
     assert not codegen.is_ahead_of_time(codegen.kernel_point(GemmConfig(block_m=224, m_fast_tile_order=2, math_warpgroups=4)))
     assert not codegen.is_ahead_of_time(codegen.kernel_point(GemmConfig(block_m=128, m_fast_tile_order=2, math_warpgroups=4)))
     assert not codegen.is_ahead_of_time(codegen.kernel_point(GemmConfig(block_m=192), group_scales=True))
