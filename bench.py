@@ -57,7 +57,7 @@ TOL = 2e-3
 # DRAM traffic of the dominant launch (gemm_kernel<256, exact>, M = 8192, N = 6144, K = 7168) from one ncu capture:
 # dram__bytes_read.sum + dram__bytes_write.sum (profiles/gemm_dense_m8192_n6144_k7168.md); scaled by the channel share
 # of a rank when the weight is sharded (traffic is proportional to the channels a launch covers).
-DOMINANT_TRAFFIC_BYTES = 92.2e6 + 77.3e6
+DOMINANT_TRAFFIC_BYTES = 85.3e6 + 78.3e6
 
 
 def measured_peaks() -> tuple[float, float, str]:
