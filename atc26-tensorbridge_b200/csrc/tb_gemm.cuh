@@ -796,15 +796,18 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             };
             // Writes the turned chunk c to the staged output rows of its columns: lane -> row lane / 4 (and + 8) of the
             // chunk, 8-channel word lane % 4 of the row.
-            auto flush_turned = [&](int c) {
+            // (`swapped`: the chunk was turned by stmatrix, which keeps the 16-byte words of a row swapped around by the
+            // token index.)
+            auto flush_turned = [&](int c, bool swapped = false) {
                 const int tok = lane >> 2, part = lane & 3;
                 const int nv = t.nt * 128 + quad * 32 + part * 8;
                 const __nv_bfloat16* turned = turned_chunk();
+                const int slot = swapped ? (part ^ ((tok >> 1) & 3)) : part;
                 __syncwarp();
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int row = my_row[c * 16 + h * 8 + tok];
-                    const uint4 word = *reinterpret_cast<const uint4*>(turned + (h * 8 + tok) * 32 + part * 8);
+                    const uint4 word = *reinterpret_cast<const uint4*>(turned + (h * 8 + tok) * 32 + slot * 8);
                     if (nv < p.n && row >= 0) *reinterpret_cast<uint4*>(out_row_ptr(row) + nv) = word;
                 }
                 __syncwarp();
@@ -940,6 +943,25 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                 const int n = t.nt * 128 + n_local;
                 const bool n_ok = n < p.n;
                 const bool wide_stores = wide();
+                // Chunk c (16 token columns) of this warp's accumulator -> BF16 [token][32 channels] in the warp's shared
+                // buffer, scaled: two 16-lane loads in MMA-fragment layout, packed pairs, two stmatrix.trans (the
+                // 16-byte words of a row end up swapped around by the token index: no bank conflicts either way).
+                auto turn_chunk = [&](int c) {
+                    uint32_t lo[8], hi[8];
+                    const uint32_t addr = lane_base + acc * BM + col0 + c * 16;
+                    tmem_ld_16x256b_x2(addr, lo);
+                    tmem_ld_16x256b_x2(addr + (16u << 16), hi);
+                    tmem_ld_wait_for(lo, hi);
+                    const float2 s0 = *reinterpret_cast<const float2*>(my_scale + c * 16 + 2 * (lane & 3));
+                    const float2 s1 = *reinterpret_cast<const float2*>(my_scale + c * 16 + 8 + 2 * (lane & 3));
+                    auto pack = [](uint32_t x, uint32_t y, const float2& sc) {
+                        const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(x) * sc.x, __uint_as_float(y) * sc.y);
+                        return *reinterpret_cast<const uint32_t*>(&pair);
+                    };
+                    const uint32_t st = smem_u32(turned_chunk()) + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
+                    stmatrix_x4_trans(st, pack(lo[0], lo[1], s0), pack(lo[2], lo[3], s0), pack(hi[0], hi[1], s0), pack(hi[2], hi[3], s0));
+                    stmatrix_x4_trans(st + 512, pack(lo[4], lo[5], s1), pack(lo[6], lo[7], s1), pack(hi[4], hi[5], s1), pack(hi[6], hi[7], s1));
+                };
                 if constexpr (kAccSets == 1) if (!partial && wide_stores) {
                     // One accumulator set: everything out of tensor memory first, then the accumulator goes back to the
                     // MMA warp, then the output is written (while the next tile accumulates).
@@ -1096,24 +1118,15 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     const bool nv_ok = nv < p.n;
                     const long long step = p.n;
                     __nv_bfloat16* const out0 = p.d + static_cast<long long>(t.row0 + col0 + tok) * step + nv;
+                    const int slot = part ^ ((tok >> 1) & 3);
                     for (int c = 0; c < kCols / 16; ++c) {
                         if (c * 16 >= cols_valid) break;
-                        uint32_t v[16];
-                        tmem_ld_16(lane_base + acc * BM + col0 + c * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 s4 = *reinterpret_cast<const float4*>(my_scale + c * 16 + j4 * 4);
-                            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                turned[(j4 * 4 + e) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j4 * 4 + e]) * sv[e]);
-                        }
+                        turn_chunk(c);
                         __syncwarp();
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const int col = c * 16 + h * 8 + tok;
-                            const uint4 word = *reinterpret_cast<const uint4*>(turned + (h * 8 + tok) * 32 + part * 8);
+                            const uint4 word = *reinterpret_cast<const uint4*>(turned + (h * 8 + tok) * 32 + slot * 8);
                             if (nv_ok && col < cols_valid) *reinterpret_cast<uint4*>(out0 + (c * 16 + h * 8) * step) = word;
                         }
                         __syncwarp();
@@ -1141,21 +1154,10 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     }
                 } else if (!partial && wide_stores) {
                     // Routed rows, 16-byte words: the staged output row of every column.
-                    __nv_bfloat16* const turned = turned_chunk();
                     for (int c = 0; c < kCols / 16; ++c) {
                         if (c * 16 >= cols_valid) break;
-                        uint32_t v[16];
-                        tmem_ld_16(lane_base + acc * BM + col0 + c * 16, v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 s4 = *reinterpret_cast<const float4*>(my_scale + c * 16 + j4 * 4);
-                            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                turned[(j4 * 4 + e) * 32 + lane] = __float2bfloat16_rn(__uint_as_float(v[j4 * 4 + e]) * sv[e]);
-                        }
-                        flush_turned(c);
+                        turn_chunk(c);
+                        flush_turned(c, true);
                     }
                 } else if (!partial) {
                     for (int c = 0; c < kCols / 16; ++c) {
