@@ -218,10 +218,10 @@ int rule(const tb_problem& pr, tb_config* cfg) {
         }
         splits = std::max(1, std::min({splits, k_blocks / 2 > 0 ? k_blocks / 2 : 1, 16}));
         if (tiles > 128 || pr.group_scales) splits = 1;
-        // Sharing the tiles of the last, partial round out in K blocks (use_stream_k = 1) is never picked: the CTA that
-        // finishes a shared tile reads its partners' partial sums one L2 round trip after the other, which costs more
-        // than the idle SMs of the last round (measured at N = 6144, K = 7168: 300 against 294 us at M = 8192, 162
-        // against 153 at 4096, 83 against 79 at 2048).  The path stays for callers that ask for it.
+        // Sharing the tiles of the last, partial round among the CTAs (use_stream_k = 1) is never picked: it measures
+        // the same as whole tiles (N = 6144, K = 7168: 283 against 282 us at M = 8192, 148 against 147 at 4096, 46
+        // against 45 at 1024).  These launches run under the power cap, where the few SMs of a partial last round clock
+        // higher while the others idle, so filling the round buys no time.  The path stays for callers that ask for it.
     } else {
         // Routed rows are uneven across experts: a tile of twice the mean rows (at least 32) keeps the busy experts to
         // one or two token tiles, so their weights stream from HBM once; the extra columns cost next to nothing while
@@ -511,17 +511,20 @@ int run_gemm(cudaStream_t stream, const tb_gemm_args* a, const tb_routing* routi
 
     p.div_splits = tb::FastDiv::make(static_cast<uint32_t>(p.splits));
     const int grid = static_cast<int>(std::min<long long>(units, sms));
-    // use_stream_k = 1: the tiles of the last, partial round are shared out in even shares of K blocks.  It applies
-    // where it can pay and the kernel has the path: 256-token tiles with per-token scales, more tiles than CTAs and not
-    // a whole number of rounds, at least two K blocks of the shared tiles per CTA, 16-byte output words, a workspace for
-    // the partial sums.  Otherwise the launch runs whole tiles.
+    // use_stream_k = 1: the tiles of the last, partial round are shared out: with `left` tiles on `grid` CTAs, grid / left
+    // CTAs (at most four) take a K-block range each of one tile and reduce it among themselves.  It applies where it can
+    // pay and the kernel has the path: 256-token tiles with per-token scales, more tiles than CTAs, a last round that
+    // fills at most half of them, at least four K blocks per part, 16-byte output words, a workspace for the partial
+    // sums.  Otherwise the launch runs whole tiles.
     if (layout == TB_LAYOUT_DENSE && cfg->use_stream_k == 1 && bm == 256 && !a->group_scales && a->only_split == 0) {
         const long long tiles = units, left = tiles % grid;
-        if (tiles > grid && left > 0 && left * p.k_blocks >= 2ll * grid && grid <= tb::kMaxBalancedCtas &&
-            tiles < (1ll << 24) && a->n % 8 == 0 && reinterpret_cast<uintptr_t>(a->d) % 16 == 0 && a->workspace != nullptr &&
+        const int parts = left > 0 ? static_cast<int>(std::min<long long>({grid / left, tb::kMaxSharedParts, p.k_blocks / 4})) : 0;
+        if (tiles > grid && parts >= 2 && grid <= tb::kMaxBalancedCtas && tiles < (1ll << 24) && a->n % 8 == 0 &&
+            reinterpret_cast<uintptr_t>(a->d) % 16 == 0 && a->workspace != nullptr &&
             reinterpret_cast<uintptr_t>(a->workspace) % 16 == 0 && a->workspace_bytes >= balanced_scratch_bytes(grid)) {
             p.whole_rounds = static_cast<int>(tiles / grid);
             p.shared_tiles = static_cast<int>(left);
+            p.shared_parts = parts;
         }
     }
     const bool exact = a->bridge == TB_BRIDGE_EXACT;

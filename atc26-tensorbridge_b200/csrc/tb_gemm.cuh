@@ -47,6 +47,7 @@ constexpr int kEpochCells = 1024;  // 32-bit words at the head of the split-K wo
 constexpr int kBalancedFlag0 = 16;  // balanced launches: word kBalancedFlag0 + c is raised when CTA c has published its partial tile
 constexpr int kMaxBalancedCtas = kEpochCells - kBalancedFlag0;
 constexpr int kBalancedTileWords = 128 * 256;  // FP32 partial sums of one 128-channel x 256-token tile
+constexpr int kMaxSharedParts = 4;  // CTAs that share one tile of the last round
 constexpr int kMaxOutputPeers = 16;   // ranks whose buffers an epilogue can scatter to
 constexpr int kMaxSplitTiles = 128;  // output tiles of a K-split launch: the tile index takes 7 bits of a tag
 constexpr int kTransposeBytes = 16 * 32 * 2;  // an epilogue warp's 16-column chunk as BF16 [token][channel]
@@ -113,9 +114,10 @@ struct alignas(64) GemmParams {
     int layout, num_experts, top_k;
     int splits;    // dense: K splits (>= 1)
     // dense, 256-token tile: when shared_tiles > 0 every CTA runs whole_rounds whole tiles (tile = CTA + round x grid)
-    // and then an even share of the K blocks of the shared_tiles tiles that are left over; the CTA that holds the
-    // first K blocks of such a tile finishes it from the partial sums of the CTAs that hold the rest.
-    int whole_rounds, shared_tiles;
+    // and then CTA c takes K blocks [j, j + 1) * k_blocks / shared_parts of left-over tile c / shared_parts,
+    // j = c % shared_parts (CTAs from shared_tiles * shared_parts on are done).  The parts of a tile exchange FP32
+    // partial sums through the workspace and each finishes a share of the tile's columns.
+    int whole_rounds, shared_tiles, shared_parts;
     int a_gathered;  // indexed: `a` is already [padded routes, k] in sorted order (tb_gather_rows ran first)
     int static_weights;      // 1: no kernel in flight on the stream writes weight / scale: they may be read before
                              //    griddepcontrol.wait returns
@@ -147,8 +149,8 @@ struct Unit {
     int kb0, kb1;    // K-block range
     int tile;        // dense tile index (slot of its partial sums in the split-K workspace)
     int split;
-    int part;        // shared tiles: 0 whole tile, 1 its first K blocks (finishes the tile), 2 later K blocks (publishes)
-    int partners;    // part 1: the CTAs after this one that hold the tile's other K blocks
+    int parts;       // shared tiles: number of CTAs that hold K-block ranges of this tile (0: the whole tile is this CTA's)
+    int part;        // ... and which of them this CTA is
     bool skip;       // test hook (GemmParams::only_split): the unit is left out by every role
 };
 
@@ -390,27 +392,21 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
     }
 
     // Units of this CTA: every gridDim.x-th unit -- or, with shared tiles, an index into its whole rounds followed by
-    // the shared tiles its share of K blocks [share0, share1) touches.
+    // its part of a shared tile, if it has one.
     int u_begin = blockIdx.x, u_step = gridDim.x, u_end = total_units;
-    [[maybe_unused]] int share0 = 0, share1 = 0;
-    auto share_begin = [&](int cta) {  // first K block (counted over all shared tiles) of a CTA's share
-        return static_cast<int>(static_cast<long long>(cta) * p.shared_tiles * p.k_blocks / gridDim.x);
-    };
     if constexpr (kAccSets == 1) {
         if (p.shared_tiles > 0) {
-            share0 = share_begin(blockIdx.x);
-            share1 = share_begin(blockIdx.x + 1);
             u_begin = 0;
             u_step = 1;
-            u_end = p.whole_rounds + (share1 > share0 ? (share1 - 1) / p.k_blocks - share0 / p.k_blocks + 1 : 0);
+            u_end = p.whole_rounds + (static_cast<int>(blockIdx.x) < p.shared_tiles * p.shared_parts ? 1 : 0);
         }
     }
 
     auto decode = [&](int u) {
         Unit t;
         t.split = 0;
+        t.parts = 0;
         t.part = 0;
-        t.partners = 0;
         t.skip = false;
         t.kb0 = 0;
         t.kb1 = p.k_blocks;
@@ -418,14 +414,14 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
         if (p.layout == kDense) {
             t.tile = p.div_splits.div(u);
             t.split = u - t.tile * p.splits;
-            [[maybe_unused]] int shared_index = -1;
             if constexpr (kAccSets == 1) {
                 if (p.shared_tiles > 0) {
                     if (u < p.whole_rounds) {
                         t.tile = blockIdx.x + u * gridDim.x;
                     } else {
-                        shared_index = share0 / p.k_blocks + (u - p.whole_rounds);
-                        t.tile = p.whole_rounds * gridDim.x + shared_index;
+                        t.parts = p.shared_parts;
+                        t.part = static_cast<int>(blockIdx.x) % p.shared_parts;
+                        t.tile = p.whole_rounds * gridDim.x + static_cast<int>(blockIdx.x) / p.shared_parts;
                     }
                 }
             }
@@ -437,16 +433,9 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
             t.kb0 = p.div_splits.div(t.split * p.k_blocks);
             t.kb1 = p.div_splits.div((t.split + 1) * p.k_blocks);
             t.skip = p.only_split != 0 && t.split != p.only_split - 1;
-            if constexpr (kAccSets == 1) {
-                if (shared_index >= 0) {  // this CTA's share covers K blocks [kb0, kb1) of the shared tile
-                    t.kb0 = max(0, share0 - shared_index * p.k_blocks);
-                    t.kb1 = min(p.k_blocks, share1 - shared_index * p.k_blocks);
-                    t.part = t.kb0 > 0 ? 2 : (t.kb1 < p.k_blocks ? 1 : 0);
-                    if (t.part == 1) {
-                        const int tile_end = (shared_index + 1) * p.k_blocks;
-                        while (share_begin(blockIdx.x + 1 + t.partners) < tile_end) ++t.partners;  // the last CTA's share ends with the last tile
-                    }
-                }
+            if (t.parts > 0) {
+                t.kb0 = t.part * p.k_blocks / t.parts;
+                t.kb1 = (t.part + 1) * p.k_blocks / t.parts;
             }
         } else {
             const int g = p.div_n_tiles.div(u);
@@ -962,6 +951,136 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     stmatrix_x4_trans(st, pack(lo[0], lo[1], s0), pack(lo[2], lo[3], s0), pack(hi[0], hi[1], s0), pack(hi[2], hi[3], s0));
                     stmatrix_x4_trans(st + 512, pack(lo[4], lo[5], s1), pack(lo[6], lo[7], s1), pack(hi[4], hi[5], s1), pack(hi[6], hi[7], s1));
                 };
+                if constexpr (kAccSets == 1) if (t.parts > 0) {
+                    // A tile of the last, partial round: `parts` CTAs hold K-block ranges of it (CTAs first ... first +
+                    // parts - 1, this one is number `part`).  Every warp's eight 16-token chunks are dealt out among the
+                    // parts (chunk c belongs to part c % parts).  A part first publishes the FP32 partial sums of the
+                    // chunks it does not own -- as they come out of tensor memory, register for register, into its
+                    // slot of the workspace -- and raises its flag with the launch's tag; then it waits (bounded) for
+                    // the flags of the others and finishes its own chunks: partial sums added in part order 0, 1, ...
+                    // whoever does the adding, so the result does not depend on timing.  Nobody waits before it has
+                    // published, and all CTAs of the grid are resident: no part waits on one that waits on it.
+                    const int first_cta = static_cast<int>(blockIdx.x) - t.part;
+                    uint4* const slot0 = reinterpret_cast<uint4*>(p.workspace + kEpochCells) + warp * (8 * 4 * 32) + lane;
+                    auto slot_of = [&](int cta) { return slot0 + (static_cast<long long>(cta) * kBalancedTileWords >> 2); };
+                    const uint32_t balanced_tag = (launch_seq + 1u) & 0x1FFFFFFu;
+                    const uint32_t acc_addr = lane_base + acc * BM + col0;
+                    constexpr int kChunks = kCols / 16;
+                    uint4* const mine = slot_of(blockIdx.x);
+                    for (int c = 0; c < kChunks; ++c) {  // pass 1: publish
+                        if (c * 16 >= cols_valid) break;
+                        if (c % t.parts == t.part) continue;
+                        uint32_t lo[8], hi[8];
+                        tmem_ld_16x256b_x2(acc_addr + c * 16, lo);
+                        tmem_ld_16x256b_x2(acc_addr + c * 16 + (16u << 16), hi);
+                        tmem_ld_wait_for(lo, hi);
+                        __stcg(mine + (c * 4 + 0) * 32, make_uint4(lo[0], lo[1], lo[2], lo[3]));
+                        __stcg(mine + (c * 4 + 1) * 32, make_uint4(lo[4], lo[5], lo[6], lo[7]));
+                        __stcg(mine + (c * 4 + 2) * 32, make_uint4(hi[0], hi[1], hi[2], hi[3]));
+                        __stcg(mine + (c * 4 + 3) * 32, make_uint4(hi[4], hi[5], hi[6], hi[7]));
+                    }
+                    __threadfence();
+                    named_barrier_sync(1, kEpilogueWarps * 32);
+                    if (warp == 0 && lane == 0) {
+                        unsigned* const flags = reinterpret_cast<unsigned*>(p.workspace) + kBalancedFlag0;
+                        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + blockIdx.x), "r"(balanced_tag) : "memory");
+                        const long long start = clock64();
+                        for (int q = 0; q < t.parts && *abort_flag == 0; ++q) {
+                            if (q == t.part) continue;
+                            unsigned seen;
+                            for (uint32_t spin = 0;; ++spin) {
+                                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + first_cta + q) : "memory");
+                                if (seen == balanced_tag) break;
+                                if ((spin & 15u) == 15u && (*abort_flag != 0 || clock64() - start > p.wait_cycles)) {
+                                    atomicCAS(const_cast<int*>(abort_flag), 0, kWaitSplit);
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                    named_barrier_sync(1, kEpilogueWarps * 32);
+                    if (*abort_flag != 0) { ok = false; break; }
+                    // pass 2: this part's chunks.  Sums in part order; the own partial sums come from tensor memory.
+                    const uint32_t stage_u32 = smem_u32(turned_chunk());
+                    const uint32_t st_addr = stage_u32 + (lane & 7) * 64 + (((lane >> 3) ^ ((lane >> 1) & 3)) << 4);
+                    const float* const scale_pair = my_scale + 2 * (lane & 3);
+                    int parked = 0;  // chunks of this warp turned into shared memory (at most three: parts >= 2, one slot each)
+                    for (int c = t.part; c < kChunks; c += t.parts) {
+                        if (c * 16 >= cols_valid) break;
+                        uint32_t lo[8], hi[8];
+                        tmem_ld_16x256b_x2(acc_addr + c * 16, lo);
+                        tmem_ld_16x256b_x2(acc_addr + c * 16 + (16u << 16), hi);
+                        tmem_ld_wait_for(lo, hi);
+                        // The others' sums of the same registers, all loads in flight at once (another SM wrote them:
+                        // not through L1); then the additions in part order, the own sums in their place.
+                        constexpr int kOthers = kMaxSharedParts - 1;
+                        uint4 theirs[kOthers][4];
+#pragma unroll
+                        for (int r = 0; r < kOthers; ++r) {
+                            if (r < t.parts - 1) {
+                                const uint4* const from = slot_of(first_cta + (r < t.part ? r : r + 1)) + c * 4 * 32;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) theirs[r][i] = __ldcg(from + i * 32);
+                            }
+                        }
+                        float sum[16];
+#pragma unroll
+                        for (int q = 0; q < kMaxSharedParts; ++q) {
+                            if (q < t.parts) {
+                                float term[16];
+                                if (q == t.part) {
+#pragma unroll
+                                    for (int i = 0; i < 8; ++i) { term[i] = __uint_as_float(lo[i]); term[8 + i] = __uint_as_float(hi[i]); }
+                                } else {
+#pragma unroll
+                                    for (int r = 0; r < kOthers; ++r) {
+                                        if (r == (q < t.part ? q : q - 1)) {
+                                            const uint4* const w = theirs[r];
+                                            const uint32_t words[16] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w,
+                                                                        w[2].x, w[2].y, w[2].z, w[2].w, w[3].x, w[3].y, w[3].z, w[3].w};
+#pragma unroll
+                                            for (int i = 0; i < 16; ++i) term[i] = __uint_as_float(words[i]);
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) sum[i] = q == 0 ? term[i] : sum[i] + term[i];
+                            }
+                        }
+                        const float2 s0 = *reinterpret_cast<const float2*>(scale_pair + c * 16);
+                        const float2 s1 = *reinterpret_cast<const float2*>(scale_pair + c * 16 + 8);
+                        auto pack = [](float x, float y, const float2& sc) {
+                            const __nv_bfloat162 pair = __floats2bfloat162_rn(x * sc.x, y * sc.y);
+                            return *reinterpret_cast<const uint32_t*>(&pair);
+                        };
+                        stmatrix_x4_trans(st_addr + parked * 1024, pack(sum[0], sum[1], s0), pack(sum[2], sum[3], s0),
+                                          pack(sum[8], sum[9], s0), pack(sum[10], sum[11], s0));
+                        stmatrix_x4_trans(st_addr + parked * 1024 + 512, pack(sum[4], sum[5], s1), pack(sum[6], sum[7], s1),
+                                          pack(sum[12], sum[13], s1), pack(sum[14], sum[15], s1));
+                        ++parked;
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty(acc));
+                    {   // the output of this part's chunks: lane -> token lane / 4 (and + 8), 8-channel word lane % 4 of its row
+                        const int tok = lane >> 2, part8 = lane & 3;
+                        const int nv = t.nt * 128 + quad * 32 + part8 * 8;
+                        const uint32_t ld_addr = stage_u32 + tok * 64 + ((part8 ^ ((tok >> 1) & 3)) << 4);
+                        int slot = 0;
+                        for (int c = t.part; c < kChunks && slot < parked; c += t.parts, ++slot) {
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const int col = c * 16 + h * 8 + tok;
+                                const uint4 word = lds_128(ld_addr + slot * 1024 + h * 512);
+                                if (nv < p.n && col < cols_valid)
+                                    *reinterpret_cast<uint4*>(p.d + static_cast<long long>(t.row0 + col0 + col) * p.n + nv) = word;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
+                    continue;
+                }
                 if constexpr (kAccSets == 1) if (!partial && wide_stores) {
                     // One accumulator set: everything out of tensor memory first, then the accumulator goes back to the
                     // MMA warp, then the output is written (while the next tile accumulates).
@@ -978,34 +1097,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     uint32_t kept[kKept > 0 ? kKept * 8 : 1];
                     const uint32_t acc_addr = lane_base + acc * BM + col0;
                     const float* const scale_pair = my_scale + 2 * (lane & 3);
-                    // Shared tiles.  A CTA that holds later K blocks of a tile publishes the FP32 partial sums as they
-                    // come out of tensor memory -- register for register, so the thread that holds an element here holds
-                    // it there -- and raises its flag with the launch's tag; the CTA that holds the first K blocks waits
-                    // for the flags of the CTAs behind it that hold the rest (bounded) and adds their sums to its own
-                    // before it scales, in CTA order: always the same order of additions.
-                    uint4* const partial = reinterpret_cast<uint4*>(p.workspace + kEpochCells) +
-                        (static_cast<long long>(blockIdx.x) * kBalancedTileWords >> 2) + warp * (8 * 4 * 32) + lane;
-                    const uint32_t balanced_tag = (launch_seq + 1u) & 0x1FFFFFFu;
-                    if (t.part == 1) {
-                        if (warp == 0 && lane == 0) {
-                            const long long start = clock64();
-                            for (int q = 1; q <= t.partners; ++q) {
-                                const unsigned* const flag = reinterpret_cast<const unsigned*>(p.workspace) + kBalancedFlag0 + blockIdx.x + q;
-                                unsigned seen;
-                                for (uint32_t spin = 0;; ++spin) {
-                                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-                                    if (seen == balanced_tag) break;
-                                    if ((spin & 15u) == 15u && (*abort_flag != 0 || clock64() - start > p.wait_cycles)) {
-                                        atomicCAS(const_cast<int*>(abort_flag), 0, kWaitSplit);
-                                        break;
-                                    }
-                                }
-                                if (*abort_flag != 0) break;
-                            }
-                        }
-                        named_barrier_sync(1, kEpilogueWarps * 32);
-                        if (*abort_flag != 0) { ok = false; break; }
-                    }
                     auto step = [&](auto chunk) {
                         constexpr int c = decltype(chunk)::value;
                         if (c * 16 < cols_valid) {  // warp-uniform
@@ -1013,26 +1104,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                             tmem_ld_16x256b_x2(acc_addr + c * 16, lo);
                             tmem_ld_16x256b_x2(acc_addr + c * 16 + (16u << 16), hi);
                             tmem_ld_wait_for(lo, hi);
-                            if (t.part == 1) {  // the partners' sums of the same registers (written by other SMs: not through L1)
-                                for (int q = 1; q <= t.partners; ++q) {
-                                    const uint4* const theirs = partial + (static_cast<long long>(q) * kBalancedTileWords >> 2) + c * 4 * 32;
-                                    const uint4 q0 = __ldcg(theirs), q1 = __ldcg(theirs + 32), q2 = __ldcg(theirs + 64), q3 = __ldcg(theirs + 96);
-                                    const uint32_t w[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
-                                                            q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i) {
-                                        lo[i] = __float_as_uint(__uint_as_float(lo[i]) + __uint_as_float(w[i]));
-                                        hi[i] = __float_as_uint(__uint_as_float(hi[i]) + __uint_as_float(w[8 + i]));
-                                    }
-                                }
-                            }
-                            if (t.part == 2) {
-                                __stcg(partial + (c * 4 + 0) * 32, make_uint4(lo[0], lo[1], lo[2], lo[3]));
-                                __stcg(partial + (c * 4 + 1) * 32, make_uint4(lo[4], lo[5], lo[6], lo[7]));
-                                __stcg(partial + (c * 4 + 2) * 32, make_uint4(hi[0], hi[1], hi[2], hi[3]));
-                                __stcg(partial + (c * 4 + 3) * 32, make_uint4(hi[4], hi[5], hi[6], hi[7]));
-                                return;
-                            }
                             const float2 s0 = *reinterpret_cast<const float2*>(scale_pair + c * 16);
                             const float2 s1 = *reinterpret_cast<const float2*>(scale_pair + c * 16 + 8);
                             auto pack = [](uint32_t x, uint32_t y, const float2& sc) {
@@ -1057,16 +1128,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p) {
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty(acc));
-                    if (t.part == 2) {  // published: every warp's stores, then the flag
-                        __threadfence();
-                        named_barrier_sync(1, kEpilogueWarps * 32);
-                        if (warp == 0 && lane == 0) {
-                            unsigned* const flag = reinterpret_cast<unsigned*>(p.workspace) + kBalancedFlag0 + blockIdx.x;
-                            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(balanced_tag) : "memory");
-                        }
-                        if (++acc == kAccSets) { acc = 0; aphase ^= 1u; }
-                        continue;
-                    }
                     // The output: lane -> token lane / 4 (and + 8) of a chunk, 8-channel word lane % 4 of its row.
                     const int tok = lane >> 2, part = lane & 3;
                     const int nv = t.nt * 128 + quad * 32 + part * 8;

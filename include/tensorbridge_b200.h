@@ -43,10 +43,10 @@ enum { TB_QUANT_PER_TOKEN = 0, TB_QUANT_GROUP_128 = 1 };
  *                      64 up) once tb_register_kernel has a kernel for them
  *   num_stages         depth of the weight ring (codes + scales, 9 KB a stage), rounded down to a multiple of the
  *                      bridge teams; the token ring takes what is left of shared memory, at most 8 stages
- *   use_stream_k       dense GEMM: 0 = whole tiles; 1 = the tiles of the last, partial round are shared out in even
- *                      shares of K blocks (256-token tiles, more tiles than SMs: the CTA with a tile's first K
- *                      blocks finishes it from the FP32 partial sums of the others, added in a fixed order;
- *                      launches it does not fit run whole tiles);
+ *   use_stream_k       dense GEMM: 0 = whole tiles; 1 = the tiles of the last, partial round are shared out, two
+ *                      to four CTAs with a K-block range each per tile (256-token tiles, more tiles than SMs, a
+ *                      last round that fills at most half of them: the parts exchange FP32 partial sums and add
+ *                      them in a fixed order; launches it does not fit run whole tiles);
  *                      2..16 = that many deterministic K splits of every tile
  *   m_fast_tile_order  bridge teams that alternate K blocks: 0/1 = one team, 2 or 4
  *   block_k            128

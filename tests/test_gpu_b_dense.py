@@ -101,12 +101,13 @@ def test_dense_split_k_is_deterministic_and_correct(splits, block_m):
 
 
 @pytest.mark.parametrize("m,n,k,num_sms", [(1024, 6144, 1024, 0), (777, 6400, 1280, 0), (512, 640, 1024, 7),
-                                            (700, 384, 2048, 4), (2048, 1152, 512, 13)])
-def test_dense_even_k_block_shares(m, n, k, num_sms):
-    """`use_stream_k = 1` on the 256-token tile: every CTA takes an even share of all K blocks, and a tile cut between
-    two CTAs is finished by the first from the FP32 partial sums the second published.  Right against the oracle,
-    bit-identical from launch to launch (the two parts are always added in the same order), within an FP32 rounding of
-    the whole-tile launch -- and the launch did take the shared path (flags of the publishing CTAs carry its tag)."""
+                                            (700, 384, 2048, 4), (700, 384, 2048, 7), (2048, 1152, 1024, 17)])
+def test_dense_shared_last_round(m, n, k, num_sms):
+    """`use_stream_k = 1` on the 256-token tile: the tiles of the last, partial round are shared out, two to four CTAs
+    per tile here, each with a range of K blocks; the parts exchange FP32 partial sums and each finishes some of the
+    tile's columns.  Right against the oracle, bit-identical from launch to launch (the parts are always added in the
+    same order), within an FP32 rounding of the whole-tile launch -- and the launch did take the shared path (flags of
+    the CTAs that published carry its tag)."""
     import ctypes
     import tensorbridge as tb
     from tensorbridge import _native as native
